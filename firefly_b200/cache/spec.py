@@ -43,3 +43,12 @@ def sub_slot(slot: int, k: int) -> int:
     if not (0 <= slot < SUB_SLOT_STRIDE):
         raise ValueError(f"cache slot {slot} out of range")
     return slot + (k + 1) * SUB_SLOT_STRIDE
+
+
+FILTER_SUB_SLOT = 63
+
+
+def filter_slot(slot: int) -> int:
+    """The id of the state that a block's input filter keeps beside its mixer's cache (a mixer made of mixers uses
+    the sub-slots from 0 up)."""
+    return sub_slot(slot, FILTER_SUB_SLOT)

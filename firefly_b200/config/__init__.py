@@ -1,8 +1,9 @@
 from .base import (ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, ScheduleEntry,
                    read_config_json)
+from .kefisun import KefisunConfig
 from .kolorax import KoloraxConfig
 from .pepolorn import PepolornConfig
 from .qwen3 import Qwen3Config
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
-           "KoloraxConfig", "PepolornConfig", "Qwen3Config", "read_config_json"]
+           "KefisunConfig", "KoloraxConfig", "PepolornConfig", "Qwen3Config", "read_config_json"]

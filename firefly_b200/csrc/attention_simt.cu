@@ -10,6 +10,10 @@
 // (:173, mask on indices local to the portion) keys are taken from the cache by
 // absolute position, 0..pos, or the last `window` of them.
 //
+// A bias by distance may be taken off the scores: `dist_bias` [nq, bias_len] floats, entry (h, i - j) for query
+// position i and key position j (null: none).  The caller makes the table as long as the window, so every
+// visible key has an entry; a key further away than the table counts as masked.
+//
 // A warp takes every 4th key starting at the first visible one, so the order of
 // additions for a query depends only on its position and window, never on how the
 // tokens were cut into steps or what else is in the batch.
@@ -33,7 +37,8 @@ __global__ void paged_attention_simt_kernel(
     const T* q, int q_stride, const T* cache,
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
     const int* __restrict__ positions, T* __restrict__ out, int out_stride, int nq, int nkv, int d,
-    int block_size, int num_blocks, float scale, int window, int* __restrict__ status) {
+    int block_size, int num_blocks, float scale, int window, const float* __restrict__ dist_bias, int bias_len,
+    int* __restrict__ status) {
     pdl_prologue();
     q = pdl_fresh(q);              // the kernel in front writes the finished heads and this step's cache rows
     cache = pdl_fresh(cache);
@@ -43,8 +48,10 @@ __global__ void paged_attention_simt_kernel(
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kh = h / (nq / nkv);
     const int seq = token_seq[t], pos = positions[t];
-    const int kv_begin = first_visible_key(pos, window);
+    int kv_begin = first_visible_key(pos, window);
     const int kv_end = pos + 1;
+    const float* bias_row = dist_bias ? dist_bias + (size_t)h * bias_len : nullptr;
+    if (bias_row && kv_begin < pos - bias_len + 1) kv_begin = pos - bias_len + 1;
 
     float qr[ATT_PER_LANE], acc[ATT_PER_LANE];
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
@@ -70,7 +77,8 @@ __global__ void paged_attention_simt_kernel(
             const int i = lane + 32 * jj;
             if (i < d) part += qr[jj] * to_float(krow[i]);
         }
-        const float s = warp_sum(part) * scale;
+        float s = warp_sum(part) * scale;
+        if (bias_row) s -= bias_row[pos - j];
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);
         const float p = expf(s - m_new);
@@ -115,19 +123,20 @@ FF_EXPORT int ff_paged_attention_simt(const void* q, int dtype, int q_stride, co
                                       const int* block_table, int max_blocks, const int* token_seq,
                                       const int* positions, void* out, int out_stride, int T, int nq,
                                       int nkv, int d, int block_size, int num_blocks, float scale,
-                                      int window, int* status, cudaStream_t stream) {
+                                      int window, const float* dist_bias, int bias_len, int* status,
+                                      cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || d > ATT_MAX_D) return FF_ERR_UNSUPPORTED;
-    if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    if (nkv <= 0 || nq % nkv || (dist_bias && bias_len <= 0)) return FF_ERR_BAD_ARG;
     dim3 grid(T, nq);
     if (dtype == 0)
         FF_LAUNCH((paged_attention_simt_kernel<float>), grid, ATT_WARPS * 32, 0, stream, 
             (const float*)q, q_stride, (const float*)cache, block_table, max_blocks, token_seq,
-            positions, (float*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, status);
+            positions, (float*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, status);
     else if (dtype == 1)
         FF_LAUNCH((paged_attention_simt_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, 
             (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, token_seq,
-            positions, (bf16*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, status);
+            positions, (bf16*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, status);
     else
         return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();

@@ -1,0 +1,245 @@
+// A recurrent mixer that corrects its state by the error of its own prediction (the gated delta rule), with a
+// decay per head and key channel:
+//
+//   S_t   = diag(g_t) S_(t-1)                         S: [key channel, value channel] per head, 32-bit, starts at 0
+//   u_t   = beta_t (v_t - S_t^T k_t)
+//   S_t  += k_t u_t^T
+//   o_t   = S_t^T q_t                                  (the read-out sees the token's own write)
+//
+// with q and k made unit vectors per head on the way in (x / sqrt(sum x^2 + unit_eps), q also times q_scale),
+// beta_t = sigmoid(raw beta) and g_t[i] = exp(-exp(A_log_h) * softplus(a_t[i] + dt_bias[i])).  Everything behind
+// the projections is 32-bit.  The state lives in the request's state slot and is carried from step to step; a
+// fresh request starts from zeros.  A sequence's tokens are walked in order with the same order of additions
+// however the prompt was cut into steps.
+//
+// One block per (sequence, head, share of the value columns).  Value column j is held by PARTS neighbouring
+// threads, each with NP / PARTS key channels of column j in registers; the two sums over key channels of a
+// token (the prediction and the read-out) are joined over those threads by shuffles.
+#include "common.cuh"
+
+namespace ff {
+
+__device__ __forceinline__ float dr_softplus(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+struct DeltaArgs {
+    const void* q; int q_stride, q_off;          // rows of [groups, N]
+    const void* k; int k_stride, k_off;
+    const void* v; int v_stride, v_off;          // rows of [heads, V]
+    const void* beta; int beta_stride, beta_off; // raw, rows of [heads]
+    const float* a; int a_stride, a_off;         // raw decay inputs, rows of [heads, N], 32-bit
+    const float* dt_bias;                        // [heads * N]
+    const float* a_log;                          // [heads]
+    int heads_per_group;
+    float q_scale, unit_eps;
+};
+
+constexpr int DR_CHUNK = 8;
+constexpr int DR_MAX_THREADS = 512;
+
+struct DeltaPlan { int NP, PARTS, vsplit, Vb, threads; };
+static inline bool delta_plan(int N, int V, DeltaPlan* p) {
+    if (N <= 0 || N > 256 || V <= 0 || V > 256) return false;
+    p->NP = N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256)));
+    p->PARTS = p->NP >= 128 ? 16 : (p->NP >= 32 ? 8 : 4);
+    const int max_cols = DR_MAX_THREADS / p->PARTS;
+    p->vsplit = (V + max_cols - 1) / max_cols;
+    p->Vb = (V + p->vsplit - 1) / p->vsplit;
+    p->threads = ((p->Vb * p->PARTS + 31) / 32) * 32;
+    return true;
+}
+
+template <typename T, int NP, int PARTS>
+__global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
+    DeltaArgs A, float* __restrict__ state, size_t state_stride, int state_off, const int* __restrict__ cu_q,
+    const int* __restrict__ state_slots, const int* __restrict__ seq_fresh, float* __restrict__ o /*[T, heads*V]*/,
+    int heads, int N, int V, int Vb) {
+    pdl_prologue();
+    constexpr int KP = NP / PARTS;
+    static_assert(KP % 4 == 0, "a thread reads its key channels four at a time");
+    __shared__ __align__(16) float s_q[DR_CHUNK][NP], s_k[DR_CHUNK][NP], s_g[DR_CHUNK][NP];
+    __shared__ float s_v[DR_CHUNK][128];
+    __shared__ float s_b[DR_CHUNK];
+    const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
+    const int jl = tid / PARTS, part = tid % PARTS;
+    const int j0 = blockIdx.z * Vb, j = j0 + jl;
+    const int t0 = cu_q[s], t1 = cu_q[s + 1];
+    const bool live = jl < Vb && j < V;
+    const bool fresh = seq_fresh[s] != 0;
+    // a block's share of a head's state is kept as its threads hold it: register i of thread tid at i * threads + tid
+    float* S_g = state + (size_t)state_slots[s] * state_stride + state_off +
+                 ((size_t)h * gridDim.z + blockIdx.z) * KP * nthr;
+    float S[KP];
+#pragma unroll
+    for (int i = 0; i < KP; ++i) S[i] = fresh ? 0.f : S_g[(size_t)i * nthr + tid];
+    const int group = h / A.heads_per_group;
+    const T* qp = pdl_fresh((const T*)A.q) + A.q_off + (size_t)group * N;
+    const T* kp = pdl_fresh((const T*)A.k) + A.k_off + (size_t)group * N;
+    const T* vp = pdl_fresh((const T*)A.v) + A.v_off + (size_t)h * V + j0;
+    const T* bp = pdl_fresh((const T*)A.beta) + A.beta_off + h;
+    const float* ap = pdl_fresh(A.a) + A.a_off + (size_t)h * N;
+    const float* dtb = A.dt_bias + (size_t)h * N;
+    const int cols = min(Vb, V - j0);
+    const float rate = expf(A.a_log[h]);
+    for (int c0 = t0; c0 < t1; c0 += DR_CHUNK) {
+        const int n = min(DR_CHUNK, t1 - c0);
+        __syncthreads();
+        // staging: the chunk's q, k (raw), decays, v and beta in 32-bit
+        for (int idx = tid; idx < DR_CHUNK * NP; idx += nthr) {
+            const int c = idx / NP, i = idx - c * NP;
+            float qv = 0.f, kv = 0.f, gv = 0.f;
+            if (c < n && i < N) {
+                qv = to_float(qp[(size_t)(c0 + c) * A.q_stride + i]);
+                kv = to_float(kp[(size_t)(c0 + c) * A.k_stride + i]);
+                gv = expf(-rate * dr_softplus(ap[(size_t)(c0 + c) * A.a_stride + i] + dtb[i]));
+            }
+            s_q[c][i] = qv;
+            s_k[c][i] = kv;
+            s_g[c][i] = gv;
+        }
+        for (int idx = tid; idx < DR_CHUNK * cols; idx += nthr) {
+            const int c = idx / cols, jj = idx - c * cols;
+            s_v[c][jj] = c < n ? to_float(vp[(size_t)(c0 + c) * A.v_stride + jj]) : 0.f;
+        }
+        if (tid < DR_CHUNK)
+            s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(bp[(size_t)(c0 + tid) * A.beta_stride]))) : 0.f;
+        __syncthreads();
+        // unit vectors: a warp per token
+        for (int c = warp; c < n; c += nwarps) {
+            float sq = 0.f, sk = 0.f;
+            for (int i = lane; i < NP; i += 32) { sq += s_q[c][i] * s_q[c][i]; sk += s_k[c][i] * s_k[c][i]; }
+            sq = warp_sum(sq);
+            sk = warp_sum(sk);
+            const float fq = A.q_scale / sqrtf(sq + A.unit_eps), fk = 1.0f / sqrtf(sk + A.unit_eps);
+            for (int i = lane; i < NP; i += 32) { s_q[c][i] *= fq; s_k[c][i] *= fk; }
+        }
+        __syncthreads();
+#pragma unroll 1
+        for (int c = 0; c < n; ++c) {
+            const float vj = live ? s_v[c][jl] : 0.f;
+            const float beta = s_b[c];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < KP; i += 4) {
+                // thread `part` holds key channels 4 PARTS m + 4 part + e (m = i / 4, e < 4)
+                const int at = i * PARTS + part * 4;
+                const float4 g4 = *reinterpret_cast<const float4*>(&s_g[c][at]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
+                S[i]     *= g4.x;  d0 += k4.x * S[i];
+                S[i + 1] *= g4.y;  d1 += k4.y * S[i + 1];
+                S[i + 2] *= g4.z;  d2 += k4.z * S[i + 2];
+                S[i + 3] *= g4.w;  d3 += k4.w * S[i + 3];
+            }
+            float dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+            for (int off = 1; off < PARTS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            const float u = beta * (vj - dot);
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+#pragma unroll
+            for (int i = 0; i < KP; i += 4) {
+                const int at = i * PARTS + part * 4;
+                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[c][at]);
+                const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
+                S[i]     += k4.x * u;  a0 += q4.x * S[i];
+                S[i + 1] += k4.y * u;  a1 += q4.y * S[i + 1];
+                S[i + 2] += k4.z * u;  a2 += q4.z * S[i + 2];
+                S[i + 3] += k4.w * u;  a3 += q4.w * S[i + 3];
+            }
+            float acc = (a0 + a1) + (a2 + a3);
+#pragma unroll
+            for (int off = 1; off < PARTS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            if (live && part == 0) o[(size_t)(c0 + c) * heads * V + (size_t)h * V + j] = acc;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < KP; ++i) S_g[(size_t)i * nthr + tid] = S[i];
+}
+
+// y[t, h*V + i] = o[t, h*V + i] / sqrt(mean_i o[t, h, :]^2 + eps) * w[i] * sigmoid(gate[t, gate_off + h*V + i]):
+// a norm over each head's values with one weight row for all heads, then a sigmoid gate.  One warp per (token, head).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* o, const float* gate, int gate_stride, int gate_off,
+                                      const float* __restrict__ w, float eps, T* __restrict__ y, int rows, int heads, int V) {
+    pdl_prologue();
+    o = pdl_fresh(o);
+    gate = pdl_fresh(gate);
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const int t = row / heads, h = row - t * heads;
+    const float* orow = o + (size_t)row * V;
+    const float* grow = gate + (size_t)t * gate_stride + gate_off + (size_t)h * V;
+    float ss = 0.f;
+    for (int i = lane; i < V; i += 32) ss += orow[i] * orow[i];
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)V + eps);
+    for (int i = lane; i < V; i += 32)
+        y[(size_t)row * V + i] = from_float<T>(orow[i] * inv * w[i] / (1.0f + expf(-grow[i])));
+}
+
+}  // namespace ff
+
+using namespace ff;
+
+// floats of a request's state for `heads` heads of key size N and value size V (-1: sizes not supported)
+FF_EXPORT long long ff_delta_state_floats(int heads, int N, int V) {
+    DeltaPlan p;
+    if (!delta_plan(N, V, &p)) return -1;
+    return (long long)heads * p.vsplit * (p.NP / p.PARTS) * p.threads;
+}
+
+template <typename T>
+static int delta_launch(const DeltaArgs& A, float* state, long long state_stride, int state_off, const int* cu_q,
+                        const int* state_slots, const int* seq_fresh, float* o, int n_seqs, int heads, int N, int V,
+                        cudaStream_t stream) {
+    DeltaPlan p;
+    if (!delta_plan(N, V, &p)) return FF_ERR_UNSUPPORTED;
+    if (p.Vb > 128) return FF_ERR_UNSUPPORTED;
+    dim3 grid(n_seqs, heads, p.vsplit);
+#define FF_DELTA(NP, PARTS)                                                                                    \
+    FF_LAUNCH((delta_rule_scan_kernel<T, NP, PARTS>), grid, p.threads, 0, stream, A, state, (size_t)state_stride, \
+              state_off, cu_q, state_slots, seq_fresh, o, heads, N, V, p.Vb)
+    switch (p.NP) {
+        case 16: FF_DELTA(16, 4); break;
+        case 32: FF_DELTA(32, 8); break;
+        case 64: FF_DELTA(64, 8); break;
+        case 128: FF_DELTA(128, 16); break;
+        case 256: FF_DELTA(256, 16); break;
+        default: return FF_ERR_UNSUPPORTED;
+    }
+#undef FF_DELTA
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_delta_rule_scan(const void* q, int q_stride, int q_off, const void* k, int k_stride, int k_off,
+                                 const void* v, int v_stride, int v_off, const void* beta, int beta_stride, int beta_off,
+                                 int dtype, const float* a, int a_stride, int a_off, const float* dt_bias,
+                                 const float* a_log, int heads_per_group, float q_scale, float unit_eps, float* state,
+                                 long long state_stride, int state_off, const int* cu_q, const int* state_slots,
+                                 const int* seq_fresh, float* o, int T, int n_seqs, int heads, int N, int V,
+                                 cudaStream_t stream) {
+    if (T <= 0 || n_seqs <= 0) return 0;
+    if (heads_per_group <= 0 || heads % heads_per_group) return FF_ERR_BAD_ARG;
+    DeltaArgs A{q, q_stride, q_off, k, k_stride, k_off, v, v_stride, v_off, beta, beta_stride, beta_off,
+                a, a_stride, a_off, dt_bias, a_log, heads_per_group, q_scale, unit_eps};
+    if (dtype == 0)
+        return delta_launch<float>(A, state, state_stride, state_off, cu_q, state_slots, seq_fresh, o, n_seqs, heads, N, V, stream);
+    if (dtype == 1)
+        return delta_launch<bf16>(A, state, state_stride, state_off, cu_q, state_slots, seq_fresh, o, n_seqs, heads, N, V, stream);
+    return FF_ERR_BAD_ARG;
+}
+
+FF_EXPORT int ff_head_norm_gate(const float* o, const float* gate, int gate_stride, int gate_off, const float* w, float eps,
+                                void* y, int dtype, int T, int heads, int V, cudaStream_t stream) {
+    const int rows = T * heads;
+    if (rows <= 0) return 0;
+    const int warps = 4;
+    const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
+    if (dtype == 0)
+        FF_LAUNCH((head_norm_gate_kernel<float>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (float*)y, rows, heads, V);
+    else if (dtype == 1)
+        FF_LAUNCH((head_norm_gate_kernel<bf16>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (bf16*)y, rows, heads, V);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}

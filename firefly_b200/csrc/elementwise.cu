@@ -382,20 +382,37 @@ __global__ void norm_add_vec_kernel(float* __restrict__ residual, const TD* delt
     }
 }
 
-// out[t,i] = act(gu[t,i]) * gu[t,I+i]; act 0: SiLU, 1: the tanh form of GELU
+// out[t,i] = act(g) * u with g = gu[t,i] (+ bias[i]), u = gu[t,I+i] (+ bias[I+i]); act 0: SiLU, 1: the tanh form
+// of GELU, 2: the clamped form min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1).
+// `bias` float32 [2I] or null.
 template <typename T>
-__global__ void glu_act_kernel(const T* gu, T* __restrict__ out, int I, size_t total, int act) {
+__global__ void glu_act_kernel(const T* gu, const float* __restrict__ bias, T* __restrict__ out, int I, size_t total,
+                               int act, float limit) {
     pdl_prologue();
     gu = pdl_fresh(gu);
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const size_t t = idx / I;
     const int i = (int)(idx - t * I);
-    const float g = to_float(gu[t * 2 * I + i]), u = to_float(gu[t * 2 * I + I + i]);
+    float g = to_float(gu[t * 2 * I + i]), u = to_float(gu[t * 2 * I + I + i]);
+    if (bias) { g += bias[i]; u += bias[I + i]; }
     float a;
     if (act == 0) a = g / (1.0f + expf(-g));
-    else a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else if (act == 1) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+        a = g / (1.0f + expf(-1.702f * g));
+    }
     out[idx] = from_float<T>(a * u);
+}
+
+// x *= a
+__global__ void scale_kernel(float* x, float a, size_t total) {
+    pdl_prologue();
+    x = pdl_fresh(x);
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < total) x[idx] *= a;
 }
 }  // namespace ff
 
@@ -434,14 +451,22 @@ FF_EXPORT int ff_norm_add(float* residual, const void* delta, int delta_dtype, c
     return 0;
 }
 
-FF_EXPORT int ff_glu_act(const void* gate_up, void* out, int dtype, int T, int I, int act, cudaStream_t stream) {
+FF_EXPORT int ff_glu_act(const void* gate_up, const float* bias, void* out, int dtype, int T, int I, int act, float limit,
+                         cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
-    if (act != 0 && act != 1) return FF_ERR_BAD_ARG;
+    if (act < 0 || act > 2) return FF_ERR_BAD_ARG;
     const unsigned blocks = (unsigned)((total + 255) / 256);
-    if (dtype == 0) FF_LAUNCH((glu_act_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, (float*)out, I, total, act);
-    else if (dtype == 1) FF_LAUNCH((glu_act_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, (bf16*)out, I, total, act);
+    if (dtype == 0) FF_LAUNCH((glu_act_kernel<float>), blocks, 256, 0, stream, (const float*)gate_up, bias, (float*)out, I, total, act, limit);
+    else if (dtype == 1) FF_LAUNCH((glu_act_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)gate_up, bias, (bf16*)out, I, total, act, limit);
     else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_scale(float* x, float a, size_t n, cudaStream_t stream) {
+    if (n == 0) return 0;
+    FF_LAUNCH(scale_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, a, n);
     FF_LAUNCH_CHECK();
     return 0;
 }

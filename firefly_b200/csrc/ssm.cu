@@ -20,22 +20,27 @@ __device__ __forceinline__ float silu_f(float z) { return z / (1.0f + expf(-z));
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
 
 // ----------------------------------------------------------------------------- convolution --
-// out[t, c] = silu(bias[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]); inputs in front of the portion come
-// from the state slot (`conv_off`: [(taps-1), C] floats, oldest first; zeros for a fresh request).
+// out[t, c] = act(bias[c] + sum_j w[c, j] * in[t - (taps-1) + j, c]) (+ in[t, c]); inputs in front of the portion
+// come from the state slot (`conv_off`: [(taps-1), C] floats, oldest first; zeros for a fresh request).
+// `flags`: CONV_SILU the activation is SiLU (else none), CONV_ADD_INPUT the token's own input is added to the
+// result (a filter whose output is x + conv(x)).  `bias` may be null.  The output type TO may differ from the
+// input's (32-bit rows in, rows of the engine's type out).
 // A thread takes VEC neighbouring channels (one 16-byte load where the layout allows it, else one channel)
 // and walks `tile` tokens with the last taps-1 inputs in registers, so every input of a long step is read once
 // (steps of few tokens get a thread a token, so that they still fill the GPU).
 constexpr int CONV_MAX_TAPS = 16;
+constexpr int CONV_SILU = 1, CONV_ADD_INPUT = 2;
 
 // TAPS > 0: the number of taps is known when the kernel is built (the window stays in registers); 0: any number
 // up to CONV_MAX_TAPS.
-template <typename T, int VEC, int TAPS>
+template <typename T, typename TO, int VEC, int TAPS>
 __global__ void causal_conv_silu_kernel(const T* in, int in_stride, int in_off,
                                         const float* __restrict__ w /*[C,taps]*/, const float* __restrict__ bias,
                                         const float* state, size_t state_stride, int conv_off,
                                         const int* __restrict__ token_seq, const int* __restrict__ cu_q,
                                         const int* __restrict__ state_slots, const int* __restrict__ seq_fresh,
-                                        T* __restrict__ out /*[T,C]*/, int Ttot, int C, int taps_rt, int tile) {
+                                        TO* __restrict__ out /*[T,C]*/, int Ttot, int C, int taps_rt, int tile,
+                                        int flags) {
     pdl_prologue();
     in = pdl_fresh(in);
     state = pdl_fresh(state);
@@ -48,7 +53,7 @@ __global__ void causal_conv_silu_kernel(const T* in, int in_stride, int in_off,
     float wt[MT][VEC], bs[VEC];
 #pragma unroll
     for (int e = 0; e < VEC; ++e) {
-        bs[e] = bias[c0 + e];
+        bs[e] = bias ? bias[c0 + e] : 0.f;
 #pragma unroll
         for (int j = 0; j < MT; ++j) wt[j][e] = j < taps ? w[(size_t)(c0 + e) * taps + j] : 0.f;
     }
@@ -101,14 +106,19 @@ __global__ void causal_conv_silu_kernel(const T* in, int in_stride, int in_off,
 #pragma unroll
                 for (int e = 0; e < VEC; ++e) acc[e] += wt[j][e] * cur[e];
             }
-        T* dst = out + (size_t)t * C + c0;
-        if constexpr (VEC == 1) dst[0] = from_float<T>(silu_f(acc[0]));
-        else {
-            uint4 raw;
-            T* v = reinterpret_cast<T*>(&raw);
 #pragma unroll
-            for (int e = 0; e < VEC; ++e) v[e] = from_float<T>(silu_f(acc[e]));
-            *reinterpret_cast<uint4*>(dst) = raw;
+        for (int e = 0; e < VEC; ++e) {
+            if (flags & CONV_SILU) acc[e] = silu_f(acc[e]);
+            if (flags & CONV_ADD_INPUT) acc[e] += cur[e];
+        }
+        TO* dst = out + (size_t)t * C + c0;
+        if constexpr (VEC == 1) dst[0] = from_float<TO>(acc[0]);
+        else {
+            struct alignas(VEC * sizeof(TO)) Pack { TO v[VEC]; };
+            Pack raw;
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) raw.v[e] = from_float<TO>(acc[e]);
+            *reinterpret_cast<Pack*>(dst) = raw;
         }
         // slide: the oldest row leaves, the current one comes in
 #pragma unroll
@@ -368,10 +378,11 @@ __global__ void gated_rms_norm_kernel(const float* o, const T* z, int z_stride, 
 
 using namespace ff;
 
-template <typename T>
+template <typename T, typename TO>
 static int conv_launch(const void* in, int in_stride, int in_off, const float* w, const float* bias, float* state,
                        long long state_stride, int conv_off, const int* token_seq, const int* cu_q, const int* state_slots,
-                       const int* seq_fresh, void* out, int T_, int n_seqs, int C, int taps, cudaStream_t stream) {
+                       const int* seq_fresh, void* out, int T_, int n_seqs, int C, int taps, int flags,
+                       cudaStream_t stream) {
     constexpr int V = 16 / (int)sizeof(T);
     const bool vec = taps >= 2 && taps <= 4 && C % V == 0 && in_off % V == 0 && in_stride % V == 0 &&
                      (((uintptr_t)in | (uintptr_t)out) & 15) == 0;
@@ -381,8 +392,9 @@ static int conv_launch(const void* in, int in_stride, int in_off, const float* w
     const int tile = T_ >= 4096 ? 16 : (T_ >= 512 ? 4 : 1);
     dim3 grid((T_ + tile - 1) / tile, (lanes + threads - 1) / threads);
 #define FF_CONV(VV, TT)                                                                                              \
-    FF_LAUNCH((causal_conv_silu_kernel<T, VV, TT>), grid, threads, 0, stream, (const T*)in, in_stride, in_off, w, bias, \
-              (const float*)state, (size_t)state_stride, conv_off, token_seq, cu_q, state_slots, seq_fresh, (T*)out, T_, C, taps, tile)
+    FF_LAUNCH((causal_conv_silu_kernel<T, TO, VV, TT>), grid, threads, 0, stream, (const T*)in, in_stride, in_off, w, bias, \
+              (const float*)state, (size_t)state_stride, conv_off, token_seq, cu_q, state_slots, seq_fresh, (TO*)out, T_, C, taps, \
+              tile, flags)
     if (vec) {
         switch (taps) {
             case 2: FF_CONV(V, 2); break;
@@ -408,19 +420,48 @@ static int conv_launch(const void* in, int in_stride, int in_off, const float* w
     return 0;
 }
 
+// `out_dtype`: the type of `out` (the input's, or the engine's type for 32-bit input rows).
+FF_EXPORT int ff_causal_conv(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* bias,
+                             float* state, long long state_stride, int conv_off, const int* token_seq,
+                             const int* cu_q, const int* state_slots, const int* seq_fresh, void* out, int out_dtype,
+                             int T, int n_seqs, int C, int taps, int flags, cudaStream_t stream) {
+    if (T <= 0 || C <= 0) return 0;
+    if (taps < 1 || taps > CONV_MAX_TAPS) return FF_ERR_UNSUPPORTED;
+#define FF_CONV_TYPES(TI, TOUT)                                                                                          \
+    return conv_launch<TI, TOUT>(in, in_stride, in_off, w, bias, state, state_stride, conv_off, token_seq, cu_q, state_slots, \
+                                 seq_fresh, out, T, n_seqs, C, taps, flags, stream)
+    if (dtype == 0 && out_dtype == 0) FF_CONV_TYPES(float, float);
+    if (dtype == 1 && out_dtype == 1) FF_CONV_TYPES(bf16, bf16);
+    if (dtype == 0 && out_dtype == 1) FF_CONV_TYPES(float, bf16);
+#undef FF_CONV_TYPES
+    return FF_ERR_BAD_ARG;
+}
+
 FF_EXPORT int ff_causal_conv_silu(const void* in, int dtype, int in_stride, int in_off, const float* w, const float* bias,
                                   float* state, long long state_stride, int conv_off, const int* token_seq,
                                   const int* cu_q, const int* state_slots, const int* seq_fresh, void* out, int T,
                                   int n_seqs, int C, int taps, cudaStream_t stream) {
-    if (T <= 0 || C <= 0) return 0;
-    if (taps < 1 || taps > CONV_MAX_TAPS) return FF_ERR_UNSUPPORTED;
+    return ff_causal_conv(in, dtype, in_stride, in_off, w, bias, state, state_stride, conv_off, token_seq, cu_q, state_slots,
+                          seq_fresh, out, dtype, T, n_seqs, C, taps, CONV_SILU, stream);
+}
+
+// Only the second half of the convolution: the last taps-1 rows of `in` of every sequence go into its state
+// slot, for a part that convolves inside a kernel of its own.
+FF_EXPORT int ff_conv_state_update(const void* in, int dtype, int in_stride, int in_off, float* state, long long state_stride,
+                                   int conv_off, const int* cu_q, const int* state_slots, const int* seq_fresh, int n_seqs,
+                                   int C, int taps, cudaStream_t stream) {
+    if (n_seqs <= 0 || C <= 0 || taps <= 1) return 0;
+    if (taps > CONV_MAX_TAPS) return FF_ERR_UNSUPPORTED;
+    const int cy = min(64, (C + 255) / 256);
     if (dtype == 0)
-        return conv_launch<float>(in, in_stride, in_off, w, bias, state, state_stride, conv_off, token_seq, cu_q, state_slots,
-                                  seq_fresh, out, T, n_seqs, C, taps, stream);
-    if (dtype == 1)
-        return conv_launch<bf16>(in, in_stride, in_off, w, bias, state, state_stride, conv_off, token_seq, cu_q, state_slots,
-                                 seq_fresh, out, T, n_seqs, C, taps, stream);
-    return FF_ERR_BAD_ARG;
+        FF_LAUNCH((conv_state_update_kernel<float>), dim3(n_seqs, cy), 256, 0, stream, (const float*)in, in_stride, in_off, state,
+                  (size_t)state_stride, conv_off, cu_q, state_slots, seq_fresh, C, taps);
+    else if (dtype == 1)
+        FF_LAUNCH((conv_state_update_kernel<bf16>), dim3(n_seqs, cy), 256, 0, stream, (const bf16*)in, in_stride, in_off, state,
+                  (size_t)state_stride, conv_off, cu_q, state_slots, seq_fresh, C, taps);
+    else return FF_ERR_BAD_ARG;
+    FF_LAUNCH_CHECK();
+    return 0;
 }
 
 // floats of a request's state for `heads` heads of key size N and value size V (-1: sizes not supported)

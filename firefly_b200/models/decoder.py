@@ -10,7 +10,7 @@ from typing import Dict, List, Mapping, Optional
 
 import torch
 
-from ..cache.spec import sub_slot
+from ..cache.spec import filter_slot, sub_slot
 from ..config.base import ModelSpec
 from ..parts import Runtime, build_part, part_class
 from ..parts.base import declared, host_synchronous
@@ -81,7 +81,7 @@ class DecoderModel:
         """What each written cache slot needs (slot id -> spec)."""
         out: Dict[int, object] = {}
         whole: Dict[int, object] = {}
-        for layer, slot, write in self.schedule:
+        for i_run, (layer, slot, write) in enumerate(self.schedule):
             if write:
                 spec = whole[slot] = self.blocks[layer].cache_spec()
                 if isinstance(spec, (tuple, list)):      # a mixer made of mixers: one cache per inner mixer
@@ -89,6 +89,11 @@ class DecoderModel:
                         out[sub_slot(slot, k)] = sub
                 else:
                     out[slot] = spec
+            # a block's input filter keeps its state whether or not the run writes the mixer's cache
+            extra = getattr(self.blocks[layer], "filter_cache_spec", None)
+            extra = extra() if callable(extra) else None
+            if extra is not None:
+                out[filter_slot(i_run)] = extra
         for layer, slot, write in self.schedule:
             if not write:
                 want = self.blocks[layer].cache_spec()
@@ -120,6 +125,8 @@ class DecoderModel:
                 residual, pending = self.junctions[j].forward(residual, pending, ctx, stream0, turn)
             # the norm that follows this run, for a last product that can fold it in
             nxt = self.blocks[runs[i + 1][0]] if i + 1 < len(runs) else None
+            if getattr(block, "input_filter", None) is not None:
+                ctx.memo["filter_slot"] = filter_slot(i)      # the filter's state belongs to the run, not to the cache it reads
             if self._takes_next_norm[layer]:
                 next_norm = nxt.first_norm() if nxt is not None and hasattr(nxt, "first_norm") else None
                 residual, pending = block.forward(residual, pending, ctx, slot, write, next_norm=next_norm)

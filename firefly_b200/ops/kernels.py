@@ -84,6 +84,8 @@ _MODULES = {
     "moe": ("moe.cu", None),
     "ssm": ("ssm.cu", None),
     "head_finish": ("head_finish.cu", None),
+    "conv_attention": ("conv_attention.cu", None),
+    "delta_rule": ("delta_rule.cu", None),
 }
 
 
@@ -217,14 +219,27 @@ def qk_norm_rope_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, q_norm_w, k
         c_int(num_blocks), _p(cache), _p(status), _stream()), "qk_norm_rope_store")
 
 
+def _check_dist_bias(dist_bias: Optional[torch.Tensor], nq: int, window: int) -> None:
+    """A table of biases by distance covers a window: one row a query head, one entry per distance the window
+    lets through."""
+    if dist_bias is None:
+        return
+    if dist_bias.dtype != torch.float32 or dist_bias.dim() != 2 or dist_bias.shape[0] != nq or not dist_bias.is_contiguous():
+        raise KernelError("attention: the bias by distance is a contiguous float32 table [query heads, distances]")
+    if window <= 0 or dist_bias.shape[1] < window:
+        raise KernelError("attention: a bias by distance needs a window no longer than its table")
+
+
 def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_table: torch.Tensor,
                          token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                          nq: int, nkv: int, d: int, scale: float, window: int,
-                         status: torch.Tensor) -> None:
+                         status: torch.Tensor, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Attention of every query token over its sequence's cached keys 0..pos
     (or the last ``window`` of them; 0 = all).  ``q`` is read with row stride
-    ``q_stride`` elements (it may be the head of a wider qkv buffer)."""
-    _need_cuda(cache, block_table, token_seq, positions, out, status)
+    ``q_stride`` elements (it may be the head of a wider qkv buffer).  ``dist_bias`` float32 [nq, L]:
+    entry (h, i - j) is taken off the score of query position i and key position j."""
+    _need_cuda(cache, block_table, token_seq, positions, out, status, dist_bias)
+    _check_dist_bias(dist_bias, nq, window)
     if not q.is_cuda:
         raise KernelError("firefly_b200 kernels run on a CUDA device only")
     T = out.shape[0]
@@ -234,8 +249,8 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bl
     _check(lib.ff_paged_attention_simt(
         _p(q), c_int(_dt(q)), c_int(q_stride), _p(cache), _p(block_table), c_int(block_table.shape[1]),
         _p(token_seq), _p(positions), _p(out), c_int(out.shape[1]), c_int(T), c_int(nq), c_int(nkv),
-        c_int(d), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status),
-        _stream()), "paged_attention_simt")
+        c_int(d), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(dist_bias),
+        c_int(dist_bias.shape[1] if dist_bias is not None else 0), _p(status), _stream()), "paged_attention_simt")
 
 
 _sample_scratch = {}
@@ -670,13 +685,15 @@ def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, pa
 
 
 def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
-                    out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int) -> None:
+                    out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int,
+                    dist_bias: Optional[torch.Tensor] = None) -> None:
     """Attention of a step's tokens over the paged cache; picks the kernel: the
     tensor-core kernels for bfloat16 and head sizes in steps of 16, the plain
-    kernel for 32-bit and every other head size up to 256."""
-    if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d):
+    kernel for 32-bit and every other head size up to 256.  ``dist_bias`` float32 [nq, L >= window]: entry
+    (h, i - j) is taken off the score of query position i and key position j."""
+    if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d) or dist_bias is not None:
         paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
-                             scale, window, ctx.status)
+                             scale, window, ctx.status, dist_bias)
         return
     G = nq // nkv
     n = ctx.num_seqs
@@ -990,16 +1007,27 @@ def norm_add(residual: torch.Tensor, delta: torch.Tensor, weight: torch.Tensor, 
            "norm_add")
 
 
-GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+GLU_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
 
 
-def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str) -> None:
-    """out[t,i] = act(gate_up[t,i]) * gate_up[t,I+i]; act: "silu" or "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))."""
-    _need_cuda(gate_up, out)
+def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, bias: Optional[torch.Tensor] = None,
+            limit: float = 0.0) -> None:
+    """out[t,i] = act(g) * u with g = gate_up[t,i] (+ bias[i]) and u = gate_up[t,I+i] (+ bias[I+i]); act: "silu",
+    "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) or "clamped_swish"
+    (min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1)).  ``bias`` float32 [2I]."""
+    _need_cuda(gate_up, out, bias)
     T, I = out.shape
     assert gate_up.shape == (T, 2 * I) and gate_up.dtype == out.dtype
-    _check(_lib("elementwise").ff_glu_act(_p(gate_up), _p(out), c_int(_dt(out)), c_int(T), c_int(I),
-                                         c_int(GLU_ACTIVATIONS[activation]), _stream()), "glu_act")
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * I)
+    _check(_lib("elementwise").ff_glu_act(_p(gate_up), _p(bias), _p(out), c_int(_dt(out)), c_int(T), c_int(I),
+                                         c_int(GLU_ACTIVATIONS[activation]), c_float(limit), _stream()), "glu_act")
+
+
+def scale_(x: torch.Tensor, a: float) -> None:
+    """x *= a for a contiguous float32 tensor."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_lib("elementwise").ff_scale(_p(x), c_float(a), c_size_t(x.numel()), _stream()), "scale")
 
 
 def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim: int, eps: float, freq: torch.Tensor,
@@ -1076,6 +1104,154 @@ def causal_conv_silu(x: torch.Tensor, col0: int, channels: int, weight: torch.Te
     global LAUNCHES
     if taps > 1:
         LAUNCHES += 1     # the kernel that saves the last inputs
+
+
+CONV_SILU, CONV_ADD_INPUT = 1, 2
+
+
+def causal_conv(x: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: Optional[torch.Tensor],
+                state: torch.Tensor, conv_off: int, ctx, out: torch.Tensor, *, silu: bool = False,
+                add_input: bool = False) -> None:
+    """`causal_conv_silu` with the activation and the bias as options: out[t,c] = act(bias[c] + sum_j weight[c,j] *
+    x[t - (taps-1) + j, col0 + c]) (+ x[t, col0 + c] with ``add_input``).  ``out`` may be of the engine's type while
+    ``x`` is 32-bit."""
+    _need_cuda(x, weight, bias, state, out)
+    T = x.shape[0]
+    taps = weight.shape[1]
+    assert weight.dtype == state.dtype == torch.float32 and weight.shape[0] == channels and state.dim() == 2
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == channels)
+    assert out.shape == (T, channels) and (out.dtype == x.dtype or x.dtype == torch.float32)
+    assert state.shape[1] >= conv_off + (taps - 1) * channels
+    _check(_lib("ssm").ff_causal_conv(
+        _p(x), c_int(_dt(x)), c_int(x.stride(0)), c_int(col0), _p(weight), _p(bias), _p(state),
+        ctypes.c_longlong(state.stride(0)), c_int(conv_off), _p(ctx.token_seq), _p(ctx.cu_q), _p(ctx.state_slots),
+        _p(ctx.seq_fresh), _p(out), c_int(_dt(out)), c_int(T), c_int(ctx.num_seqs), c_int(channels), c_int(taps),
+        c_int((CONV_SILU if silu else 0) | (CONV_ADD_INPUT if add_input else 0)), _stream()), "causal_conv")
+    global LAUNCHES
+    if taps > 1:
+        LAUNCHES += 1     # the kernel that saves the last inputs
+
+
+def conv_state_update(x: torch.Tensor, col0: int, channels: int, taps: int, state: torch.Tensor, conv_off: int, ctx) -> None:
+    """The last taps-1 rows of x[:, col0 : col0 + channels] of every sequence into its state slot ([taps-1, channels]
+    floats at ``conv_off``), for a part that convolves inside a kernel of its own."""
+    _need_cuda(x, state)
+    assert state.dtype == torch.float32 and state.shape[1] >= conv_off + (taps - 1) * channels
+    if taps <= 1:
+        return
+    _check(_lib("ssm").ff_conv_state_update(
+        _p(x), c_int(_dt(x)), c_int(x.stride(0)), c_int(col0), _p(state), ctypes.c_longlong(state.stride(0)),
+        c_int(conv_off), _p(ctx.cu_q), _p(ctx.state_slots), _p(ctx.seq_fresh), c_int(ctx.num_seqs), c_int(channels),
+        c_int(taps), _stream()), "conv_state_update")
+
+
+# --------------------------------------------------------------------------- #
+# attention heads behind a short convolution and a norm over the whole projection (csrc/conv_attention.cu)
+def conv_norm_store(proj: torch.Tensor, col0: int, conv_w: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor,
+                    eps: float, state: torch.Tensor, conv_off: int, ctx, table: torch.Tensor, pages: torch.Tensor,
+                    q_out: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, d: int, *, mix: int = 0,
+                    mix_factor: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None) -> None:
+    """q | k | v from column ``col0`` of ``proj`` pass a causal convolution per channel (``conv_w`` [C, taps], no bias,
+    the inputs in front of a portion from the state slot), q and k an RMS norm over their whole projection with the
+    weights given; q goes to ``q_out`` [T, heads * d], k and v into ``pages`` [blocks, 2, kv_heads, block, d] (heads
+    filled up to d with zeros).  ``mix`` 1: the values are also kept in ``shared`` float32 [T, kv_heads * dv];
+    2: v <- (1 - f) v + f shared with f = ``mix_factor`` (one float32 on the device).  The state is not updated
+    here (`conv_state_update`)."""
+    _need_cuda(proj, conv_w, q_norm_w, k_norm_w, state, table, pages, q_out, mix_factor, shared)
+    T = proj.shape[0]
+    C = heads * dk + kv_heads * (dk + dv)
+    taps = conv_w.shape[1]
+    num_blocks, two, ckv, block_size, cd = pages.shape
+    assert two == 2 and ckv == kv_heads and cd == d and pages.dtype == proj.dtype == q_out.dtype
+    assert conv_w.shape[0] == C and conv_w.dtype == torch.float32 and conv_w.is_contiguous()
+    assert q_norm_w.numel() == heads * dk and k_norm_w.numel() == kv_heads * dk and q_out.shape == (T, heads * d)
+    assert state.dtype == torch.float32 and state.shape[1] >= conv_off + (taps - 1) * C
+    assert shared is None or (shared.dtype == torch.float32 and shared.shape == (T, kv_heads * dv))
+    _check(_lib("conv_attention").ff_conv_norm_store(
+        _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(col0), _p(conv_w), _p(q_norm_w), _p(k_norm_w), _p(state),
+        ctypes.c_longlong(state.stride(0)), c_int(conv_off), _p(ctx.token_seq), _p(ctx.cu_q), _p(ctx.positions),
+        _p(ctx.state_slots), _p(ctx.seq_fresh), _p(table), c_int(table.shape[1]), c_int(block_size), c_int(num_blocks),
+        c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_int(d), c_int(taps), c_float(eps), c_int(mix),
+        _p(mix_factor), _p(shared), _p(q_out), _p(pages), _p(ctx.status), _stream()), "conv_norm_store")
+
+
+def head_gate(att: torch.Tensor, gate, y: torch.Tensor, heads: int, d: int, dv: int) -> None:
+    """y[t, h*dv + i] = att[t, h*d + i] * sigmoid(g[t, h*dv + i]) for i < dv; ``gate`` = (matrix, first column)."""
+    gm, g0 = gate
+    _need_cuda(att, gm, y)
+    T = y.shape[0]
+    assert att.shape == (T, heads * d) and y.shape == (T, heads * dv) and att.dtype == gm.dtype == y.dtype
+    assert att.is_contiguous() and gm.stride(1) == 1
+    _check(_lib("conv_attention").ff_head_gate(_p(att), _p(gm), c_int(gm.stride(0)), c_int(g0), c_int(_dt(y)), _p(y),
+                                              c_int(T), c_int(heads), c_int(d), c_int(dv), _stream()), "head_gate")
+
+
+# --------------------------------------------------------------------------- #
+# the gated delta rule with a decay per key channel (csrc/delta_rule.cu)
+def delta_plan(N: int, V: int):
+    """(key size the kernel is built for, threads that share a value column, blocks a head's columns are split over,
+    columns a block, threads a block): the twin of `delta_plan` in csrc/delta_rule.cu (`delta_state_floats` is the
+    kernel's own figure)."""
+    if not (0 < N <= 256 and 0 < V <= 256):
+        raise KernelError(f"delta rule: key size {N} / value size {V} not supported (up to 256 each)")
+    pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else (128 if N <= 128 else 256)))
+    parts = 16 if pad >= 128 else (8 if pad >= 32 else 4)
+    max_cols = 512 // parts
+    vsplit = -(-V // max_cols)
+    vb = -(-V // vsplit)
+    return pad, parts, vsplit, vb, -(-(vb * parts) // 32) * 32
+
+
+def delta_state_floats_plan(heads: int, N: int, V: int) -> int:
+    """Floats of a request's state for `heads` heads of key size N and value size V (worked out on the host)."""
+    pad, parts, vsplit, _, threads = delta_plan(N, V)
+    return heads * vsplit * (pad // parts) * threads
+
+
+def delta_state_floats(heads: int, N: int, V: int) -> int:
+    """Floats of a request's state for `heads` heads of key size N and value size V, in the kernel's own layout."""
+    fn = _lib("delta_rule").ff_delta_state_floats
+    fn.restype = ctypes.c_longlong
+    n = int(fn(c_int(heads), c_int(N), c_int(V)))
+    if n < 0:
+        raise KernelError(f"delta rule: key size {N} / value size {V} not supported (up to 256 each)")
+    return n
+
+
+def delta_rule_scan(q, k, v, beta, a, dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, state_off: int,
+                    ctx, o: torch.Tensor, heads: int, N: int, V: int, *, heads_per_group: int = 1, q_scale: float = 1.0,
+                    unit_eps: float = 1e-6) -> None:
+    """S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q per head, token by token.  ``q``, ``k``, ``v``,
+    ``beta``, ``a``: (matrix [T, *], first column); a q/k row holds [groups, N] (made unit vectors here, q also times
+    ``q_scale``), a v row [heads, V], a beta row [heads] (its sigmoid is taken here), an ``a`` row float32
+    [heads, N] with g = exp(-exp(a_log) softplus(a + dt_bias)).  ``state`` float32 [slots, *]: `delta_state_floats`
+    floats from ``state_off``; o float32 [T, heads * V]."""
+    (qm, q0), (km, k0), (vm, v0), (bm, b0), (am, a0) = q, k, v, beta, a
+    _need_cuda(qm, km, vm, bm, am, dt_bias, a_log, state, o)
+    T = o.shape[0]
+    assert qm.dtype == km.dtype == vm.dtype == bm.dtype and am.dtype == torch.float32
+    assert all(m.stride(1) == 1 for m in (qm, km, vm, bm, am))
+    assert dt_bias.dtype == a_log.dtype == torch.float32 and dt_bias.numel() == heads * N and a_log.numel() == heads
+    assert o.dtype == torch.float32 and o.shape == (T, heads * V) and state.dtype == torch.float32
+    _check(_lib("delta_rule").ff_delta_rule_scan(
+        _p(qm), c_int(qm.stride(0)), c_int(q0), _p(km), c_int(km.stride(0)), c_int(k0), _p(vm), c_int(vm.stride(0)),
+        c_int(v0), _p(bm), c_int(bm.stride(0)), c_int(b0), c_int(_dt(qm)), _p(am), c_int(am.stride(0)), c_int(a0),
+        _p(dt_bias), _p(a_log), c_int(heads_per_group), c_float(q_scale), c_float(unit_eps), _p(state),
+        ctypes.c_longlong(state.stride(0)), c_int(state_off), _p(ctx.cu_q), _p(ctx.state_slots), _p(ctx.seq_fresh),
+        _p(o), c_int(T), c_int(ctx.num_seqs), c_int(heads), c_int(N), c_int(V), _stream()), "delta_rule_scan")
+
+
+def head_norm_gate(o: torch.Tensor, gate, weight: torch.Tensor, eps: float, y: torch.Tensor, heads: int, V: int) -> None:
+    """y[t, h, :] = rms_norm(o[t, h, :]) * weight * sigmoid(g[t, h, :]): the norm over each head's V values, one weight
+    row [V] for all heads; ``gate`` = (float32 matrix, first column)."""
+    gm, g0 = gate
+    _need_cuda(o, gm, weight, y)
+    T = o.shape[0]
+    assert o.dtype == gm.dtype == weight.dtype == torch.float32 and weight.numel() == V and gm.stride(1) == 1
+    assert o.shape == (T, heads * V) and y.shape == o.shape and o.is_contiguous() and y.is_contiguous()
+    _check(_lib("delta_rule").ff_head_norm_gate(_p(o), _p(gm), c_int(gm.stride(0)), c_int(g0), _p(weight), c_float(eps),
+                                               _p(y), c_int(_dt(y)), c_int(T), c_int(heads), c_int(V), _stream()),
+           "head_norm_gate")
 
 
 def scalar_decay_scan(q, k, v, state: torch.Tensor, state_off: int, ctx, o: torch.Tensor, heads: int, N: int, V: int, *,

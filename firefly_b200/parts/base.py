@@ -22,6 +22,9 @@ Categories and what each must offer (beyond ``weight_specs`` and ``bind``):
 * ``junction``      runs between two layer runs where the schedule says so (the head of a pass
                     over a looped range of layers): ``forward(residual, pending, ctx, stream0,
                     turn) -> (residual, pending)``.
+* ``filter``        sits between a block's first norm and its mixer: ``cache_spec()`` -> StateSpec | None,
+                    ``wants_float32_input`` (bool) and ``forward(x, ctx, slot) -> x'`` [T, hidden] in the
+                    activation type.  A block that holds one keeps its state under a cache id of its own.
 * ``embedding``     ``forward(ctx) -> residual`` float32 [T, hidden].
 * ``head``          ``forward(x_rows) -> logits`` float32 [rows, vocab].
 
@@ -65,7 +68,7 @@ import torch
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "junction")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "junction", "filter")
 _REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

@@ -2,6 +2,10 @@
 
 ``pre_norm`` is the reference's (src/model/qwen_model.cu:106-175):
     h += mixer(norm_0(h));  h += feed_forward(norm_1(h))
+A block may hold an *input filter* (``LayerSpec.params["input_filter"]``, a PartSpec of category ``filter``): what
+the mixer reads is then filter(norm_0(h)), e.g. a short causal convolution over time added to its own input.  The
+filter's state lives under a cache id of its own per run (``cache.spec.filter_slot``).  A ``pre_norm`` block without
+a feed-forward ends after the mixer.
 The residual stream ``h`` is 32-bit.  A part's output is not added at once: it is
 handed on as ``pending`` and the next norm adds it while it reads the row, so
 each sum is done once, in 32-bit, without a pass of its own.
@@ -30,6 +34,8 @@ class Block:
         self.feed_forward = build_part("feed_forward", layer_spec.feed_forward, rt) \
             if layer_spec.feed_forward is not None else None
         self.params = dict(getattr(layer_spec, "params", None) or {})
+        self.input_filter = build_part("filter", self.params["input_filter"], rt) \
+            if self.params.get("input_filter") is not None else None
         want_norms = self.n_norms if self.feed_forward is not None else self.n_norms - 1
         if len(layer_spec.norms) != want_norms:
             raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {want_norms} norms, "
@@ -53,10 +59,22 @@ class Block:
                 nrm.fold_tag = f"fold.{k}"      # scratch of the folded form, one per norm of the block
 
     def parts(self) -> List[Part]:
-        out = [p for p in (self.mixer, self.feed_forward, *self.norms) if p is not None]
+        out = [p for p in (self.mixer, self.feed_forward, *self.norms, self.input_filter) if p is not None]
         if self.position is not None:
             out.append(self.position)
         return out
+
+    def filter_cache_spec(self):
+        """What the input filter keeps per request (None: no filter, or one without state)."""
+        return self.input_filter.cache_spec() if self.input_filter is not None else None
+
+    def _filtered_norm(self, norm, residual, pending, ctx):
+        """norm_0 followed by the input filter; the norm's rows stay 32-bit on the way where the filter wants that."""
+        if getattr(self.input_filter, "wants_float32_input", False) and ctx.dtype != torch.float32:
+            x = norm.forward(residual, pending, ctx, tag="normed.f32", out_dtype=torch.float32)
+        else:
+            x = norm.forward(residual, pending, ctx)
+        return self.input_filter.forward(x, ctx, ctx.memo["filter_slot"])
 
     def weight_specs(self) -> List[WeightSpec]:
         return [w for p in self.parts() for w in p.weight_specs()]
@@ -83,24 +101,33 @@ class PreNormBlock(Block):
     takes_next_norm = True
 
     def first_norm(self):
-        """The norm a block in front of this one may fold into its last product."""
-        return self.norms[0]
+        """The norm a block in front of this one may fold into its last product (none when a filter reads the
+        norm's rows: they must exist)."""
+        return None if self.input_filter is not None else self.norms[0]
 
     def parts(self) -> list:
         """The parts this block holds."""
-        return [p for p in (self.mixer, self.feed_forward, *self.norms, getattr(self, "position", None)) if p is not None]
+        return [p for p in (self.mixer, self.feed_forward, *self.norms, getattr(self, "position", None),
+                            getattr(self, "input_filter", None)) if p is not None]
 
     def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool, next_norm=None):
         # only a foldable norm knows ``may_defer`` (hand a folded norm on to a consumer that finishes it)
+        has_ffn = self.feed_forward is not None
         defer0 = {"may_defer": True} if self._norm_folds[0] and self._mixer_defers else {}
-        defer1 = {"may_defer": True} if self._norm_folds[1] and self._ffn_defers else {}
-        x = self.norms[0].forward(residual, pending, ctx, **defer0)
+        defer1 = {"may_defer": True} if has_ffn and self._norm_folds[1] and self._ffn_defers else {}
+        if self.input_filter is not None:
+            x = self._filtered_norm(self.norms[0], residual, pending, ctx)
+        else:
+            x = self.norms[0].forward(residual, pending, ctx, **defer0)
         kw = {}
         if self._mixer_fuses:
             kw["accumulate_into"] = residual
-            if self._mixer_folds:
-                kw["then_norm"] = self.norms[1]
+            following = self.norms[1] if has_ffn else next_norm
+            if self._mixer_folds and following is not None:
+                kw["then_norm"] = following
         a = self.mixer.forward(x, ctx, slot, write_cache, **kw)
+        if not has_ffn:              # a block of a mixer only: its delta (or folded norm) goes to the next block
+            return residual, a
         x = self.norms[1].forward(residual, a, ctx, **defer1)
         kw = {}
         if self._ffn_fuses:

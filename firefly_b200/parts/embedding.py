@@ -50,6 +50,7 @@ class LMHead(Part):
         self.hidden = int(self.p("hidden_size"))
         self.tied_to = self.p("tied_to", None)
         self.tensor = self.p("tensor", None) or self.name("weight")   # full tensor name, if it is not <prefix>.weight
+        self.scale = float(self.p("scale", 1.0))                      # the logits times this, in 32-bit
         self.weight = None
 
     def weight_specs(self) -> List[WeightSpec]:
@@ -65,6 +66,8 @@ class LMHead(Part):
         out = ctx.workspace.get("logits", (x_rows.shape[0], self.vocab), torch.float32)
         if x_rows.shape[0]:
             apply_linear(x_rows, self.weight, out, ctx, "logits")
+            if self.scale != 1.0:
+                K.scale_(out, self.scale)
         return out
 
 

@@ -71,11 +71,14 @@ class SwiGLUMLP(Part):
 
 
 class GatedMLP(Part):
-    """W_down (act(W_gate x) * (W_up x)) with the activation as a parameter ("silu" or "gelu_tanh") and the
+    """W_down (act(W_gate x) * (W_up x)) with the activation as a parameter ("silu", "gelu_tanh", or
+    "clamped_swish": min(g, limit) * sigmoid(1.702 min(g, limit)) * (clamp(u, -limit, limit) + 1)) and the
     tensors' leaves under the prefix as parameters (``gate_leaf``, ``up_leaf``, ``down_leaf``).  Gate and up are one
-    product against the stacked matrix [gate rows | up rows]; the activation is a kernel of its own.
+    product against the stacked matrix [gate rows | up rows]; the activation is a kernel of its own.  With
+    ``bias`` every projection has a bias (leaf + ``bias_suffix``), added in 32-bit: gate's and up's where the
+    activation reads them, down's into the 32-bit stream.
 
-    Parameters: hidden_size, intermediate_size, activation."""
+    Parameters: hidden_size, intermediate_size, activation, limit, bias, bias_suffix."""
 
     adds_into_residual = True        # forward(accumulate_into=...)
 
@@ -87,12 +90,23 @@ class GatedMLP(Part):
         if self.activation not in K.GLU_ACTIVATIONS:
             raise ValueError(f"{self.prefix}: activation '{self.activation}' is not one of {sorted(K.GLU_ACTIVATIONS)}")
         self.leaves = tuple(self.p(k, d) for k, d in (("gate_leaf", "gate"), ("up_leaf", "up"), ("down_leaf", "down")))
-        self.w_gate_up = self.w_down = None
+        self.limit = float(self.p("limit", 0.0))
+        self.has_bias = bool(self.p("bias", False))
+        self.bias_suffix = str(self.p("bias_suffix", ".b"))
+        if self.activation == "clamped_swish" and not (self.limit > 0):
+            raise ValueError(f"{self.prefix}: the clamped activation needs a positive limit")
+        self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
 
     def weight_specs(self) -> List[WeightSpec]:
         g, u, d = (self.name(leaf) for leaf in self.leaves)
-        return [WeightSpec(g, (self.inter, self.hidden)), WeightSpec(u, (self.inter, self.hidden)),
-                WeightSpec(d, (self.hidden, self.inter))]
+        out = [WeightSpec(g, (self.inter, self.hidden)), WeightSpec(u, (self.inter, self.hidden)),
+               WeightSpec(d, (self.hidden, self.inter))]
+        if self.has_bias:
+            sfx = self.bias_suffix
+            out += [WeightSpec(g + sfx, (self.inter,), init="zeros", as_float32=True),
+                    WeightSpec(u + sfx, (self.inter,), init="zeros", as_float32=True),
+                    WeightSpec(d + sfx, (self.hidden,), init="zeros", as_float32=True)]
+        return out
 
     def fused_layout(self, dtype_of) -> List[FusedSpec]:
         g, u, _ = (self.name(leaf) for leaf in self.leaves)
@@ -108,14 +122,29 @@ class GatedMLP(Part):
                 a, b = a.to(torch.float32), b.to(torch.float32)
             self.w_gate_up = torch.cat([a, b], dim=0).contiguous()
         self.w_down = self._matrix(tensors[d])
+        if self.has_bias:
+            sfx = self.bias_suffix
+            self.b_gate_up = torch.cat([self._vector32(tensors[g + sfx]), self._vector32(tensors[u + sfx])]).contiguous()
+            self.b_down = self._vector32(tensors[d + sfx])
 
     def forward(self, x, ctx, accumulate_into=None):
         T = x.shape[0]
         gu = ctx.workspace.get("mlp.gate_up", (T, 2 * self.inter), ctx.dtype)
         apply_linear(x, self.w_gate_up, gu, ctx, "mlp.gate_up")
         act = ctx.workspace.get("mlp.act", (T, self.inter), ctx.dtype)
-        K.glu_act(gu, act, self.activation)
-        return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
+        K.glu_act(gu, act, self.activation, self.b_gate_up, self.limit)
+        left = linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
+        if not self.has_bias:
+            return left
+        if left is None:                         # the product went into the 32-bit stream: so does its bias
+            K.add_row_vector(accumulate_into, self.b_down)
+            return None
+        if left.dtype != torch.float32:          # a delta in the engine's type: widened, so that the bias is not rounded
+            wide = ctx.workspace.get("mlp.down.f32", tuple(left.shape), torch.float32)
+            K.cast(left, wide)
+            left = wide
+        K.add_row_vector(left, self.b_down)
+        return left
 
 
 register_part("feed_forward", "swiglu_mlp", SwiGLUMLP)

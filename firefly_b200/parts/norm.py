@@ -68,16 +68,17 @@ class RMSNorm(Part):
         return xw, self.weight, ssq
 
     def forward(self, residual: torch.Tensor, delta, ctx, *, tag: str = "normed",
-                row_idx: Optional[torch.Tensor] = None, may_defer: bool = False):
+                row_idx: Optional[torch.Tensor] = None, may_defer: bool = False, out_dtype=None):
         """Adds ``delta`` (a tensor, None, or a FoldedNorm: then the residual is already updated) into
-        the residual and returns the normalised rows.  With ``may_defer`` a FoldedNorm made for this
-        very norm is handed on as it is, for the consumer's first product to finish."""
+        the residual and returns the normalised rows (in ``out_dtype``; by default the engine's type).  With
+        ``may_defer`` a FoldedNorm made for this very norm is handed on as it is, for the consumer's first
+        product to finish."""
         if isinstance(delta, FoldedNorm):
             if may_defer and delta.norm is self and row_idx is None:
                 return delta
             delta = None
         rows = residual.shape[0] if row_idx is None else row_idx.numel()
-        out = ctx.workspace.get(tag, (rows, self.size), ctx.dtype)
+        out = ctx.workspace.get(tag, (rows, self.size), out_dtype or ctx.dtype)
         K.add_rms_norm(residual, delta, self.weight, self.eps, out, row_idx)
         return out
 
