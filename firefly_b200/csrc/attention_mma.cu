@@ -129,9 +129,13 @@ struct WarpState {
     // Qs: this warp's 16 rows of q in smem ([16][KSTR]); Ks/Vs: this warp's KN keys.
     // key0: absolute index of the warp's first key.  Row r of the fragment (g, g+8)
     // sees keys in [lo[r], hi[r]); scores are multiplied by scale_log2 (= scale*log2 e).
+    // BIAS: a bias by distance is taken off the scores; brow[r] points at the entry of distance 0 of row r's
+    // head, shifted by the row's position (brow[r][-key] is the entry of key `key`), or is null for a row
+    // that is not kept.  The table covers the window, so every visible key has an entry.
+    template <bool BIAS>
     __device__ __forceinline__ void step(const bf16* Qs, const bf16* Ks, const bf16* Vs, int key0,
                                          const int (&lo)[2], const int (&hi)[2], float scale_log2,
-                                         bool need_mask) {
+                                         bool need_mask, const float* const (&brow)[2]) {
         const int lane = threadIdx.x & 31;
         float s[KN / 8][4];
 #pragma unroll
@@ -158,9 +162,13 @@ struct WarpState {
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 float v = s[j][e] * scale_log2;
+                const int key = key0 + j * 8 + 2 * t4 + (e & 1);
+                bool visible = true;
                 if (need_mask) {
-                    const int key = key0 + j * 8 + 2 * t4 + (e & 1);
-                    if (key < lo[r] || key >= hi[r]) v = -CUDART_INF_F;
+                    if (key < lo[r] || key >= hi[r]) { v = -CUDART_INF_F; visible = false; }
+                }
+                if constexpr (BIAS) {
+                    if (visible && brow[r] != nullptr) v -= *(brow[r] - key) * LOG2E;
                 }
                 s[j][e] = v;
                 mx[r] = fmaxf(mx[r], v);
@@ -228,7 +236,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride,
                   int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window,
-                  int* __restrict__ status) {
+                  const float* __restrict__ dist_bias, int bias_len, int* __restrict__ status) {
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][KSTR]
@@ -299,12 +307,14 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
     // this thread's two rows
     const int g = lane >> 2;
     int lo[2], hi[2];
+    const float* brow[2] = {nullptr, nullptr};
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int rg = row0 + warp * 16 + g + 8 * r;
         const int pos = ctx + min(rg, rows - 1) / G;
         hi[r] = pos + 1;
         lo[r] = first_visible_key(pos, window);
+        if (dist_bias) brow[r] = dist_bias + (size_t)(kh * G + min(rg, rows - 1) % G) * bias_len + pos;
     }
     const bool warp_active = row0 + warp * 16 < rows;
     // keys below this are visible to every row of the warp, keys at or above need the mask
@@ -331,8 +341,12 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
         const int key0 = t * BN;
         if (warp_active && key0 <= warp_last_pos && key0 + BN > warp_lo) {   // warp-uniform
             const bool need_mask = key0 + BN > warp_first_pos + 1 || key0 < full_lo || key0 < kv_lo;
-            st.step(Qs + warp * 16 * KSTR, Ks + buf * BN * KSTR, Vs + buf * BN * KSTR, key0, lo, hi,
-                    scale_log2, need_mask);
+            if (dist_bias)
+                st.template step<true>(Qs + warp * 16 * KSTR, Ks + buf * BN * KSTR, Vs + buf * BN * KSTR, key0, lo, hi,
+                                       scale_log2, need_mask, brow);
+            else
+                st.template step<false>(Qs + warp * 16 * KSTR, Ks + buf * BN * KSTR, Vs + buf * BN * KSTR, key0, lo, hi,
+                                        scale_log2, need_mask, brow);
         }
         __syncthreads();
     }
@@ -372,6 +386,8 @@ struct DecodeHeads {
     int max_positions;
     bf16* cache_w;             // the cache again, to write the newest key and value
     int* status;               // 2: page of the newest token missing, 3: position beyond the table, 4: a key's page missing
+    const float* dist_bias;    // [nq][bias_len] or null: a bias by distance taken off the scores (see WarpState::step)
+    int bias_len;
 };
 constexpr int HC = D / 64;     // elements of each half of a head that a lane holds (heads finished in a warp)
 
@@ -635,6 +651,14 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     }
 
     int lo[2] = {kv_lo, kv_lo}, hi[2] = {kv_hi, kv_hi};
+    const float* brow[2] = {nullptr, nullptr};
+    if (hd.dist_bias) {
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int row = (lane >> 2) + 8 * r;
+            if (row < G) brow[r] = hd.dist_bias + (size_t)(kh * G + row) * hd.bias_len + pos;
+        }
+    }
     WarpState<16> st;
     st.init();
     for (int t = t_begin; t < t_end; ++t) {
@@ -668,8 +692,12 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
         const int key0 = t * BN + warp * 16;
         if (key0 < kv_hi && key0 + 16 > kv_lo) {
             const bool need_mask = key0 + 16 > kv_hi || key0 < kv_lo;
-            st.step(Qs, Ks + (buf * BN + warp * 16) * KSTR, Vs + (buf * BN + warp * 16) * KSTR, key0, lo, hi,
-                    scale_log2, need_mask);
+            if (hd.dist_bias)
+                st.template step<true>(Qs, Ks + (buf * BN + warp * 16) * KSTR, Vs + (buf * BN + warp * 16) * KSTR, key0, lo,
+                                       hi, scale_log2, need_mask, brow);
+            else
+                st.template step<false>(Qs, Ks + (buf * BN + warp * 16) * KSTR, Vs + (buf * BN + warp * 16) * KSTR, key0, lo,
+                                        hi, scale_log2, need_mask, brow);
         }
         if (look) s_row_off[buf][threadIdx.x] = off_next;
         __syncthreads();
@@ -725,9 +753,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                    int block_size, int num_blocks, float scale_log2, int window, int num_splits,
-                   int* __restrict__ status) {
+                   const float* __restrict__ dist_bias, int bias_len, int* __restrict__ status) {
     DecodeHeads hd{};
     hd.status = status;           // may be null: a missing page is then not reported
+    hd.dist_bias = dist_bias;
+    hd.bias_len = bias_len;
     attn_decode_body<false, false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
                                    part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits,
                                    hd, DecodeUnits{});
@@ -929,14 +959,15 @@ FF_EXPORT int ff_attn_block_m() { return BM; }
 FF_EXPORT int ff_attn_tiled(const void* q, int q_stride, const void* cache, const int* block_table,
                             int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs,
                             int total_tiles, void* out, int out_stride, int nq, int nkv, int block_size,
-                            int num_blocks, float scale, int window, int* status, cudaStream_t stream) {
+                            int num_blocks, float scale, int window, const float* dist_bias, int bias_len,
+                            int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
-    if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    if (nkv <= 0 || nq % nkv || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     FF_SMEM_LIMIT(attn_tiled_kernel, TILED_SMEM);
     dim3 grid(total_tiles, nkv);
     FF_LAUNCH((attn_tiled_kernel), grid, NTHREADS, TILED_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, n_seqs,
-        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window, status);
+        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window, dist_bias, bias_len, status);
     FF_LAUNCH_CHECK();
     return 0;
 }
@@ -947,15 +978,16 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
                              int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
                              int out_stride, float* part_o, float* part_ml, int nq, int nkv,
                              int block_size, int num_blocks, float scale, int window, int num_splits,
-                             int* status, cudaStream_t stream) {
+                             const float* dist_bias, int bias_len, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
-    if (nkv <= 0 || nq % nkv || num_splits < 1) return FF_ERR_BAD_ARG;
+    if (nkv <= 0 || nq % nkv || num_splits < 1 || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
     FF_SMEM_LIMIT(attn_decode_kernel, DECODE_SMEM);
     dim3 grid(n_seqs, nkv, num_splits);
     FF_LAUNCH((attn_decode_kernel), grid, NTHREADS, DECODE_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
-        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits, status);
+        out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits, dist_bias,
+        bias_len, status);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
@@ -1015,9 +1047,10 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
                                    int nkv, int block_size, int num_blocks, float scale, int window, int units,
                                    int max_ranges, int finish_heads, const float* q_norm_w,
                                    const float* k_norm_w, float eps, const float* cos_sin, int max_positions,
-                                   int* status, cudaStream_t stream) {
+                                   const float* dist_bias, int bias_len, int* status, cudaStream_t stream) {
     if (FF_KV_PLANES != 2 && finish_heads) return FF_ERR_UNSUPPORTED;
     if (n_seqs <= 0) return 0;
+    if (dist_bias && (window <= 0 || bias_len < window)) return FF_ERR_BAD_ARG;
     if (nkv <= 0 || nq % nkv || units < n_seqs || n_seqs > NTHREADS || max_ranges < 1 || seq_ranges == nullptr)
         return FF_ERR_BAD_ARG;
     // the share-out multiplies (units - n_seqs) by a count of tiles: both within 31 bits together
@@ -1027,7 +1060,7 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
     if (finish_heads && (D % 64 != 0 || status == nullptr)) return FF_ERR_UNSUPPORTED;
     FF_SMEM_LIMIT(attn_decode_units_kernel<true>, DECODE_SMEM);
     FF_SMEM_LIMIT(attn_decode_units_kernel<false>, DECODE_SMEM);
-    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status};
+    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status, dist_bias, bias_len};
     DecodeUnits un{n_seqs, max_ranges, seq_ranges, units};
     dim3 grid(nkv, units);
     if (finish_heads)

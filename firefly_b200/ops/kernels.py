@@ -480,29 +480,37 @@ def mma_attention_supported(dtype: torch.dtype, d: int) -> bool:
     return dtype == torch.bfloat16 and d % 16 == 0 and 16 <= d <= 256
 
 
+def _bias_args(dist_bias: Optional[torch.Tensor], nq: int, window: int):
+    _check_dist_bias(dist_bias, nq, window)
+    return _p(dist_bias), c_int(dist_bias.shape[1] if dist_bias is not None else 0)
+
+
 def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale,
-               window, status: Optional[torch.Tensor] = None) -> None:
+               window, status: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """Tensor-core attention for any mix of sequences (bfloat16).  ``status`` (int32 [1]) is set to 4
-    when a key that must be read has no valid page in the block table."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out, status)
+    when a key that must be read has no valid page in the block table.  ``dist_bias``: as for
+    `paged_attention_simt`."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, status, dist_bias)
     num_blocks, planes, _, block_size, _ = pages.shape
     _check(_attn_lib(d, planes).ff_attn_tiled(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
-        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), _stream()), "attn_tiled")
+        c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), *_bias_args(dist_bias, nq, window),
+        _p(status), _stream()), "attn_tiled")
 
 
 def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, nq, nkv, d,
-                scale, window, num_splits, status: Optional[torch.Tensor] = None) -> None:
-    """Split-KV tensor-core attention when every sequence has one token (bfloat16).  ``status`` as
-    for `attn_tiled`."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status)
+                scale, window, num_splits, status: Optional[torch.Tensor] = None,
+                dist_bias: Optional[torch.Tensor] = None) -> None:
+    """Split-KV tensor-core attention when every sequence has one token (bfloat16).  ``status`` and
+    ``dist_bias`` as for `attn_tiled`."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status, dist_bias)
     num_blocks, planes, _, block_size, _ = pages.shape
     _check(_attn_lib(d, planes).ff_attn_decode(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits),
-        _p(status), _stream()), "attn_decode")
+        *_bias_args(dist_bias, nq, window), _p(status), _stream()), "attn_decode")
     global LAUNCHES
     if num_splits > 1:
         LAUNCHES += 1     # the kernel that joins the splits
@@ -663,7 +671,8 @@ def _decode_scratch(ws, n: int, nq: int, nkv: int, d: int, splits: int):
 
 
 def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, seq_ranges,
-                      nq, nkv, d, scale, window, units, max_ranges, heads=None, status=None) -> None:
+                      nq, nkv, d, scale, window, units, max_ranges, heads=None, status=None,
+                      dist_bias: Optional[torch.Tensor] = None) -> None:
     """Split-KV decode attention with `units` blocks per kv head shared out among the sequences
     in proportion to their lengths.  ``heads = (q_norm_w, k_norm_w, eps, cos_sin)``: q is the raw
     q|k|v projection and the kernel finishes the heads itself."""
@@ -671,13 +680,14 @@ def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, pa
     num_blocks, planes, _, block_size, _ = pages.shape
     assert part_o.numel() >= n_seqs * nq * units * d and part_ml.numel() >= n_seqs * nq * units * 2
     qw, kw, eps, cos_sin = heads if heads is not None else (None, None, 0.0, None)
-    _need_cuda(qw, kw, cos_sin, status)
+    _need_cuda(qw, kw, cos_sin, status, dist_bias)
     _check(_attn_lib(d, planes).ff_attn_decode_units(
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), _p(seq_ranges), c_int(nq),
         c_int(nkv), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(units),
         c_int(max_ranges), c_int(1 if heads is not None else 0), _p(qw), _p(kw), c_float(eps), _p(cos_sin),
-        c_int(cos_sin.shape[0] if cos_sin is not None else 0), _p(status), _stream()), "attn_decode_units")
+        c_int(cos_sin.shape[0] if cos_sin is not None else 0), *_bias_args(dist_bias, nq, window), _p(status),
+        _stream()), "attn_decode_units")
     global LAUNCHES, BY_LENGTH_CALLS
     BY_LENGTH_CALLS += 1
     if units > n_seqs and max_ranges > 1:
@@ -691,7 +701,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
     tensor-core kernels for bfloat16 and head sizes in steps of 16, the plain
     kernel for 32-bit and every other head size up to 256.  ``dist_bias`` float32 [nq, L >= window]: entry
     (h, i - j) is taken off the score of query position i and key position j."""
-    if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d) or dist_bias is not None:
+    if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d):
         paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
                              scale, window, ctx.status, dist_bias)
         return
@@ -705,10 +715,11 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         part_o, part_ml, seq_ranges = _decode_scratch(ctx.workspace, n_dec, nq, nkv, d, splits)
         if units:
             attn_decode_units(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml,
-                              seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES, status=ctx.status)
+                              seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES, status=ctx.status,
+                              dist_bias=dist_bias)
         else:
             attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv,
-                        d, scale, window, splits, ctx.status)
+                        d, scale, window, splits, ctx.status, dist_bias)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         # every layer of a step asks the same of the step's arrays: worked out once and kept with the step
@@ -719,7 +730,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
             if memo is not None:
                 memo[("attn_tail", id(table), n_dec)] = tail
         table_t, cu_q_t, ctx_lens_t = tail
-        if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
+        if USE_TC_ATTENTION and dist_bias is None and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
             plan = memo.get(("attn_tc_plan", G, nkv, n_dec, ctx.captured)) if memo is not None else None
             if plan is None:
                 tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
@@ -741,7 +752,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec,
-                       tiles, out, nq, nkv, d, scale, window, ctx.status)
+                       tiles, out, nq, nkv, d, scale, window, ctx.status, dist_bias)
 
 
 # --------------------------------------------------------------------------- #
