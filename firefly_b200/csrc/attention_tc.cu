@@ -215,7 +215,10 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride, int nq,
                int nkv, int block_size, int num_blocks, float scale_log2, int window, int* __restrict__ status,
-               int num_splits, float* __restrict__ part_o, float* __restrict__ part_ml) {
+               int num_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
+               const float* __restrict__ dist_bias, int bias_len) {
+    // dist_bias (float [nq][bias_len >= window], or null): entry (head, i - j) is taken off the scaled score of
+    // query position i and key position j; a window lets only distances below `window` through.
     // num_splits > 1: the grid holds every (row tile, kv head) num_splits times; each copy walks its share
     // of the tile's keys and leaves an unnormalised result with its (reference max, sum) for the join
     // kernel.  For prompts so short that their row tiles would leave most SMs idle while each block
@@ -365,6 +368,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         const int last_pos = ctx + min(q_len - 1, (row0 + BM - 1) / G);
         const int full_lo = first_visible_key(last_pos, window);
         const uint32_t lane_base = (uint32_t)((warp * 32) << 16);
+        // with a bias the scores are scaled and biased as they leave tensor memory; what follows sees scale 1
+        const float* brow = dist_bias ? dist_bias + (size_t)head * bias_len + pos : nullptr;   // brow[-key]
+        const float sl2 = dist_bias ? 1.0f : scale_log2;
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -381,7 +387,13 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             tm_ld_wait();
             // mask (only tiles that touch the diagonal or a window's edge), then the row max of the raw
             // scores with four independent chains; the scale (> 0) is applied later
-            if (need_mask) {
+            if (brow) {
+#pragma unroll
+                for (int i = 0; i < BN; ++i) {
+                    const int key = key0 + i;
+                    s[i] = (key < lo || key >= hi) ? -CUDART_INF_F : fmaf(s[i], scale_log2, -__ldg(brow - key) * LOG2E);
+                }
+            } else if (need_mask) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const int key = key0 + i;
@@ -391,7 +403,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             float mx4[4] = {s[0], s[1], s[2], s[3]};
 #pragma unroll
             for (int i = 4; i < BN; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], s[i]);
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * sl2;
             // The reference max `m` follows the true row max lazily: it moves (and O is rescaled) only
             // when the true max has grown by more than 2^8 since, which keeps p <= 256 and makes the
             // rescale rare after the first tiles.
@@ -409,7 +421,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int e = 0; e < BN / 2; ++e) {
-                w[e] = exp2_bf16x2(fmaf(s[2 * e], scale_log2, neg_m), fmaf(s[2 * e + 1], scale_log2, neg_m));
+                w[e] = exp2_bf16x2(fmaf(s[2 * e], sl2, neg_m), fmaf(s[2 * e + 1], sl2, neg_m));
                 sum4[e & 3] += __uint_as_float(w[e] << 16) + __uint_as_float(w[e] & 0xffff0000u);
             }
             // Tensor memory is written only between products: the last P V must be complete before P
@@ -689,9 +701,9 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
                          const int* cu_q, const int* ctx_lens, int n_seqs, int total_tiles, void* out,
                          int out_stride, int nq, int nkv, int block_size, int num_blocks, float scale, int window,
                          int* status, int num_splits, float* part_o, float* part_ml, int tok_base, int n_tokens,
-                         cudaStream_t stream) {
+                         const float* dist_bias, int bias_len, cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
-    if (nkv <= 0 || nq % nkv) return FF_ERR_BAD_ARG;
+    if (nkv <= 0 || nq % nkv || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || n_tokens <= 0 || tok_base < 0))) return FF_ERR_BAD_ARG;
     if (num_splits > JOIN_MAX_SPLITS) return FF_ERR_UNSUPPORTED;
     if (block_size < 8 || BN % block_size) return FF_ERR_UNSUPPORTED;
@@ -708,7 +720,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if ((long long)total_tiles * nkv * num_splits >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
     FF_LAUNCH((attn_tc_kernel), dim3((unsigned)(total_tiles * nkv * num_splits)), ATC_THREADS, ATC_SMEM, stream, arg,
               (const bf16*)q, q_stride, block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv,
-              block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml);
+              block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml, dist_bias, bias_len);
     if (num_splits > 1) {
         const int n_pairs = n_tokens * nq, per_block = JOIN_THREADS / (D / 4);
         FF_LAUNCH((attn_tc_join_kernel), dim3((unsigned)((n_pairs + per_block - 1) / per_block)), JOIN_THREADS, 0, stream,

@@ -21,6 +21,8 @@ constexpr int CA_MAX_TAPS = 16;
 struct ConvHeadArgs {
     const void* proj; int stride, col0;          // q | k | v from column col0
     const float* w;                              // [C, taps]
+    const float* w_t;                            // the same transposed, [taps, C], or null (the 16-byte form reads this one)
+    int T, tokens_per_block;                     // the 16-byte form walks this many neighbouring tokens a block
     const float* wq; const float* wk;            // [Cq], [Ck]
     const float* state; long long state_stride; int conv_off;
     const int* token_seq; const int* cu_q; const int* positions; const int* state_slots; const int* seq_fresh;
@@ -99,6 +101,131 @@ __global__ void conv_norm_store_kernel(ConvHeadArgs A, T* __restrict__ q_out /*[
     }
 }
 
+// The bfloat16 form for sizes in steps of 8 (dk, dv, d, the projection's stride and first column; at most 8192
+// channels): a thread owns eight neighbouring channels, which lie in one head of q, k or v, keeps their sums in
+// registers, reads the projection 16 bytes at a time and writes each head's part with one 16-byte store.  The
+// arithmetic, element by element, is that of the kernel above.  The weights come transposed ([taps, C]) so that
+// neighbouring threads read neighbouring addresses, and stay in registers while the block walks its tokens.
+template <int TAPS>
+__global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q_out, bf16* __restrict__ cache) {
+    pdl_prologue();
+    __shared__ float scratch[32];
+    const bf16* proj = pdl_fresh((const bf16*)A.proj);
+    const float* state = pdl_fresh(A.state);
+    const float* shared_in = pdl_fresh((const float*)A.shared);
+    const int Cq = A.H * A.dk, Ck = A.G * A.dk, Cv = A.G * A.dv, C = Cq + Ck + Cv;
+    constexpr int keep = TAPS - 1;
+    const int c = threadIdx.x * 8;
+    const bool active = c < C;
+    // the thread's weights stay in registers for all of the block's tokens
+    float wr[TAPS][8];
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+        const float4 a = active ? __ldg(reinterpret_cast<const float4*>(A.w_t + (size_t)j * C + c)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        const float4 b = active ? __ldg(reinterpret_cast<const float4*>(A.w_t + (size_t)j * C + c + 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        wr[j][0] = a.x; wr[j][1] = a.y; wr[j][2] = a.z; wr[j][3] = a.w;
+        wr[j][4] = b.x; wr[j][5] = b.y; wr[j][6] = b.z; wr[j][7] = b.w;
+    }
+    const int t_end = min(A.T, (int)(blockIdx.x + 1) * A.tokens_per_block);
+#pragma unroll 1
+    for (int t = blockIdx.x * A.tokens_per_block; t < t_end; ++t) {
+    const int s = A.token_seq[t], t0 = A.cu_q[s], pos = A.positions[t];
+    const bool fresh = A.seq_fresh[s] != 0;
+    const float* st = state + (size_t)A.state_slots[s] * A.state_stride + A.conv_off;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (active) {
+        float u[TAPS][8];
+#pragma unroll
+        for (int j = 0; j < TAPS; ++j) {
+            const int tt = t - keep + j;
+            if (tt >= t0) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)tt * A.stride + A.col0 + c);
+                const bf16* r = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) u[j][e] = __bfloat162float(r[e]);
+            } else if (!fresh) {
+                const float* row = st + (size_t)(keep + (tt - t0)) * C + c;
+                *reinterpret_cast<float4*>(&u[j][0]) = *reinterpret_cast<const float4*>(row);
+                *reinterpret_cast<float4*>(&u[j][4]) = *reinterpret_cast<const float4*>(row + 4);
+            } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) u[j][e] = 0.f;
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) acc[e] += wr[j][e] * u[j][e];
+        }
+    }
+    float ssq = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ssq += acc[e] * acc[e];
+    const float ssq_q = block_sum(active && c < Cq ? ssq : 0.f, scratch);
+    const float ssq_k = block_sum(active && c >= Cq && c < Cq + Ck ? ssq : 0.f, scratch);
+    const float inv_q = 1.0f / sqrtf(ssq_q / (float)Cq + A.eps);
+    const float inv_k = 1.0f / sqrtf(ssq_k / (float)Ck + A.eps);
+    const int page = A.block_table[(size_t)s * A.max_blocks + pos / A.block_size];
+    const bool page_ok = page >= 0 && page < A.num_blocks;
+    if (!page_ok && threadIdx.x == 0) atomicExch(A.status, 3);
+    const size_t plane = (size_t)A.G * A.block_size * A.d;
+    bf16* krow0 = cache + (size_t)(page_ok ? page : 0) * 2 * plane + (size_t)(pos % A.block_size) * A.d;
+    bf16* qrow = q_out + (size_t)t * A.H * A.d;
+    if (active) {
+        uint4 ov;
+        bf16* o = reinterpret_cast<bf16*>(&ov);
+        if (c < Cq + Ck) {
+            const bool is_q = c < Cq;
+            const int cc = is_q ? c : c - Cq;
+            const float* nw = (is_q ? A.wq : A.wk) + cc;
+            const float inv = is_q ? inv_q : inv_k;
+            const float4 w0 = __ldg(reinterpret_cast<const float4*>(nw)), w1 = __ldg(reinterpret_cast<const float4*>(nw + 4));
+            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e] * inv * ww[e]);
+            const int h = cc / A.dk, i = cc - h * A.dk;
+            if (is_q) *reinterpret_cast<uint4*>(qrow + (size_t)h * A.d + i) = ov;
+            else if (page_ok) *reinterpret_cast<uint4*>(krow0 + (size_t)h * A.block_size * A.d + i) = ov;
+        } else {
+            const int cc = c - Cq - Ck;
+            if (A.mix == 1) {
+                float* dst = A.shared + (size_t)t * Cv + cc;
+                *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            } else if (A.mix == 2) {
+                const float lam = A.lambda[0];
+                const float* src = shared_in + (size_t)t * Cv + cc;
+                const float4 s0 = *reinterpret_cast<const float4*>(src), s1 = *reinterpret_cast<const float4*>(src + 4);
+                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[e] = (1.0f - lam) * acc[e] + lam * sv[e];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+            const int g = cc / A.dv, i = cc - g * A.dv;
+            if (page_ok) *reinterpret_cast<uint4*>(krow0 + plane + (size_t)g * A.block_size * A.d + i) = ov;
+        }
+    }
+    // heads filled up to d with zeros
+    const bf16 zero = __float2bfloat16_rn(0.f);
+    if (A.d > A.dk) {
+        const int pad = A.d - A.dk;
+        for (int idx = threadIdx.x; idx < (A.H + A.G) * pad; idx += blockDim.x) {
+            const int h = idx / pad, i = A.dk + (idx - h * pad);
+            if (h < A.H) qrow[(size_t)h * A.d + i] = zero;
+            else if (page_ok) krow0[(size_t)(h - A.H) * A.block_size * A.d + i] = zero;
+        }
+    }
+    if (A.d > A.dv && page_ok) {
+        const int pad = A.d - A.dv;
+        for (int idx = threadIdx.x; idx < A.G * pad; idx += blockDim.x) {
+            const int g = idx / pad, i = A.dv + (idx - g * pad);
+            krow0[plane + (size_t)g * A.block_size * A.d + i] = zero;
+        }
+    }
+    }   // the block's tokens
+}
+
 // y[t, h*dv + i] = att[t, h*d + i] * sigmoid(g[t, g_off + h*dv + i])      (i < dv; the attention's heads have d >= dv elements)
 template <typename T>
 __global__ void head_gate_kernel(const T* att, const T* g, int g_stride, int g_off, T* __restrict__ y, int H, int d, int dv,
@@ -116,6 +243,28 @@ __global__ void head_gate_kernel(const T* att, const T* g, int g_stride, int g_o
     y[idx] = from_float<T>(a / (1.0f + expf(-z)));
 }
 
+// The same with eight bfloat16 elements a thread (dv, d, g_stride and g_off multiples of 8, 16-byte aligned rows).
+__global__ void head_gate_vec8_kernel(const bf16* att, const bf16* g, int g_stride, int g_off, bf16* __restrict__ y, int H,
+                                      int d, int dv) {
+    pdl_prologue();
+    att = pdl_fresh(att);
+    g = pdl_fresh(g);
+    const int W = H * dv;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    const size_t t = blockIdx.y;
+    if (c >= W) return;
+    const int h = c / dv, i = c - h * dv;
+    const uint4 av = *reinterpret_cast<const uint4*>(att + t * (size_t)H * d + (size_t)h * d + i);
+    const uint4 gv = *reinterpret_cast<const uint4*>(g + t * (size_t)g_stride + g_off + c);
+    const bf16* a = reinterpret_cast<const bf16*>(&av);
+    const bf16* z = reinterpret_cast<const bf16*>(&gv);
+    uint4 ov;
+    bf16* o = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(__bfloat162float(a[j]) / (1.0f + expf(-__bfloat162float(z[j]))));
+    *reinterpret_cast<uint4*>(y + t * (size_t)W + c) = ov;
+}
+
 }  // namespace ff
 
 using namespace ff;
@@ -126,7 +275,7 @@ FF_EXPORT int ff_conv_norm_store(const void* proj, int dtype, int stride, int co
                                  const int* seq_fresh, const int* block_table, int max_blocks, int block_size,
                                  int num_blocks, int T, int H, int G, int dk, int dv, int d, int taps, float eps, int mix,
                                  const float* lambda, float* shared, void* q_out, void* cache, int* status,
-                                 cudaStream_t stream) {
+                                 const float* w_t, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || d < dk || d < dv || taps < 1 || mix < 0 || mix > 2) return FF_ERR_BAD_ARG;
     if (taps > CA_MAX_TAPS) return FF_ERR_UNSUPPORTED;
@@ -135,9 +284,23 @@ FF_EXPORT int ff_conv_norm_store(const void* proj, int dtype, int stride, int co
     const int C = H * dk + G * dk + G * dv;
     const size_t smem = (size_t)C * sizeof(float);
     if (smem > 200 * 1024) return FF_ERR_UNSUPPORTED;
-    ConvHeadArgs A{proj, stride, col0, w, wq, wk, state, state_stride, conv_off, token_seq, cu_q, positions, state_slots,
+    // long steps give a block four neighbouring tokens: three of a token's four rows were read by the token in front
+    const int per_block = T >= 8192 ? 4 : 1;
+    ConvHeadArgs A{proj, stride, col0, w, w_t, T, per_block, wq, wk, state, state_stride, conv_off, token_seq, cu_q, positions, state_slots,
                    seq_fresh, block_table, max_blocks, block_size, num_blocks, H, G, dk, dv, d, taps, eps, mix, lambda,
                    shared, status};
+    if (dtype == 1 && w_t && ((uintptr_t)w_t & 15) == 0 && taps >= 2 && taps <= 4 && dk % 8 == 0 && dv % 8 == 0 && d % 8 == 0 && stride % 8 == 0 && col0 % 8 == 0 &&
+        C <= 8192 && state_stride % 4 == 0 && conv_off % 4 == 0 &&
+        (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)state | (uintptr_t)shared | (uintptr_t)wq |
+          (uintptr_t)wk) & 15) == 0) {
+        const int vthreads = (C / 8 + 31) / 32 * 32;
+        const int vblocks = (T + per_block - 1) / per_block;
+        if (taps == 2) FF_LAUNCH((conv_norm_store_vec8_kernel<2>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
+        else if (taps == 3) FF_LAUNCH((conv_norm_store_vec8_kernel<3>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
+        else FF_LAUNCH((conv_norm_store_vec8_kernel<4>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
+        FF_LAUNCH_CHECK();
+        return 0;
+    }
     const int threads = C >= 2048 ? 256 : (C >= 512 ? 128 : 64);
     if (dtype == 0) {
         if (smem > 48 * 1024) FF_SMEM_LIMIT(conv_norm_store_kernel<float>, smem);
@@ -155,6 +318,13 @@ FF_EXPORT int ff_head_gate(const void* att, const void* g, int g_stride, int g_o
     const size_t total = (size_t)T * H * dv;
     if (total == 0) return 0;
     if (d < dv) return FF_ERR_BAD_ARG;
+    if (dtype == 1 && dv % 8 == 0 && d % 8 == 0 && g_stride % 8 == 0 && g_off % 8 == 0 && T <= 65535 &&
+        (((uintptr_t)att | (uintptr_t)g | (uintptr_t)y) & 15) == 0) {
+        FF_LAUNCH(head_gate_vec8_kernel, dim3((H * dv / 8 + 127) / 128, T), 128, 0, stream, (const bf16*)att, (const bf16*)g,
+                  g_stride, g_off, (bf16*)y, H, d, dv);
+        FF_LAUNCH_CHECK();
+        return 0;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0) FF_LAUNCH((head_gate_kernel<float>), blocks, 256, 0, stream, (const float*)att, (const float*)g, g_stride, g_off, (float*)y, H, d, dv, total);
     else if (dtype == 1) FF_LAUNCH((head_gate_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)att, (const bf16*)g, g_stride, g_off, (bf16*)y, H, d, dv, total);

@@ -5,6 +5,7 @@
 //   u_t   = beta_t (v_t - S_t^T k_t)
 //   S_t  += k_t u_t^T
 //   o_t   = S_t^T q_t                                  (the read-out sees the token's own write)
+//         = (diag(g_t) S_(t-1))^T q_t + u_t (k_t . q_t)      the form the kernel uses: both sums over key channels in one walk
 //
 // with q and k made unit vectors per head on the way in (x / sqrt(sum x^2 + unit_eps), q also times q_scale),
 // beta_t = sigmoid(raw beta) and g_t[i] = exp(-exp(A_log_h) * softplus(a_t[i] + dt_bias[i])).  Everything behind
@@ -58,7 +59,7 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     static_assert(KP % 4 == 0, "a thread reads its key channels four at a time");
     __shared__ __align__(16) float s_q[DR_CHUNK][NP], s_k[DR_CHUNK][NP], s_g[DR_CHUNK][NP];
     __shared__ float s_v[DR_CHUNK][128];
-    __shared__ float s_b[DR_CHUNK];
+    __shared__ float s_b[DR_CHUNK], s_kq[DR_CHUNK];
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int jl = tid / PARTS, part = tid % PARTS;
@@ -106,48 +107,56 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
         __syncthreads();
         // unit vectors: a warp per token
         for (int c = warp; c < n; c += nwarps) {
-            float sq = 0.f, sk = 0.f;
-            for (int i = lane; i < NP; i += 32) { sq += s_q[c][i] * s_q[c][i]; sk += s_k[c][i] * s_k[c][i]; }
+            float sq = 0.f, sk = 0.f, kq = 0.f;
+            for (int i = lane; i < NP; i += 32) {
+                sq += s_q[c][i] * s_q[c][i];
+                sk += s_k[c][i] * s_k[c][i];
+                kq += s_q[c][i] * s_k[c][i];
+            }
             sq = warp_sum(sq);
             sk = warp_sum(sk);
+            kq = warp_sum(kq);
             const float fq = A.q_scale / sqrtf(sq + A.unit_eps), fk = 1.0f / sqrtf(sk + A.unit_eps);
             for (int i = lane; i < NP; i += 32) { s_q[c][i] *= fq; s_k[c][i] *= fk; }
+            if (lane == 0) s_kq[c] = kq * fq * fk;
         }
         __syncthreads();
 #pragma unroll 1
         for (int c = 0; c < n; ++c) {
             const float vj = live ? s_v[c][jl] : 0.f;
             const float beta = s_b[c];
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
+            // one walk over the decayed state gives both sums over key channels: the prediction S^T k and the
+            // read-out of the state before the write, S^T q; the write k u^T then adds u (k . q) to the read-out
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
 #pragma unroll
             for (int i = 0; i < KP; i += 4) {
                 // thread `part` holds key channels 4 PARTS m + 4 part + e (m = i / 4, e < 4)
                 const int at = i * PARTS + part * 4;
                 const float4 g4 = *reinterpret_cast<const float4*>(&s_g[c][at]);
                 const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
-                S[i]     *= g4.x;  d0 += k4.x * S[i];
-                S[i + 1] *= g4.y;  d1 += k4.y * S[i + 1];
-                S[i + 2] *= g4.z;  d2 += k4.z * S[i + 2];
-                S[i + 3] *= g4.w;  d3 += k4.w * S[i + 3];
+                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[c][at]);
+                S[i]     *= g4.x;  d0 += k4.x * S[i];      a0 += q4.x * S[i];
+                S[i + 1] *= g4.y;  d1 += k4.y * S[i + 1];  a1 += q4.y * S[i + 1];
+                S[i + 2] *= g4.z;  d2 += k4.z * S[i + 2];  a2 += q4.z * S[i + 2];
+                S[i + 3] *= g4.w;  d3 += k4.w * S[i + 3];  a3 += q4.w * S[i + 3];
             }
-            float dot = (d0 + d1) + (d2 + d3);
+            float dot = (d0 + d1) + (d2 + d3), acc = (a0 + a1) + (a2 + a3);
 #pragma unroll
-            for (int off = 1; off < PARTS; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            for (int off = 1; off < PARTS; off <<= 1) {
+                dot += __shfl_xor_sync(0xffffffffu, dot, off);
+                acc += __shfl_xor_sync(0xffffffffu, acc, off);
+            }
             const float u = beta * (vj - dot);
-            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            acc += u * s_kq[c];
 #pragma unroll
             for (int i = 0; i < KP; i += 4) {
                 const int at = i * PARTS + part * 4;
-                const float4 q4 = *reinterpret_cast<const float4*>(&s_q[c][at]);
                 const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
-                S[i]     += k4.x * u;  a0 += q4.x * S[i];
-                S[i + 1] += k4.y * u;  a1 += q4.y * S[i + 1];
-                S[i + 2] += k4.z * u;  a2 += q4.z * S[i + 2];
-                S[i + 3] += k4.w * u;  a3 += q4.w * S[i + 3];
+                S[i]     += k4.x * u;
+                S[i + 1] += k4.y * u;
+                S[i + 2] += k4.z * u;
+                S[i + 3] += k4.w * u;
             }
-            float acc = (a0 + a1) + (a2 + a3);
-#pragma unroll
-            for (int off = 1; off < PARTS; off <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
             if (live && part == 0) o[(size_t)(c0 + c) * heads * V + (size_t)h * V + j] = acc;
         }
     }

@@ -1,7 +1,7 @@
 """Throughput of a design beside the closest existing model at equal size: Kolorax beside Qwen3 dense, Pepolorn
-beside Kolorax.
+beside Kolorax, Kefisun beside Qwen3 dense.
 
-``python bench.py --design kolorax`` (or ``pepolorn``) calls `main` here; the default workload of bench.py is untouched.
+``python bench.py --design kolorax`` (or ``pepolorn``, ``kefisun``) calls `main` here; the default workload of bench.py is untouched.
 For each size, both models are built with seeded random weights at layer sizes that resemble a real
 model's (same width, same number of layers, the dense feed-forward as wide as the experts a token
 uses plus the shared one) and run through the engine's own loop (`Engine`: scheduler, captured decode
@@ -290,6 +290,8 @@ def pepolorn_kernel_table(width: int, ff: int, batch: int, prompt: int, peaks: d
 def main(args, peaks: dict) -> int:
     if args.design == "pepolorn":
         return pepolorn_main(args, peaks)
+    if args.design == "kefisun":
+        return kefisun_main(args, peaks)
     out = {"design": "Kolorax", "beside": "Qwen3 dense at equal width, layers and feed-forward width per token",
            "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
            "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
@@ -317,5 +319,184 @@ def pepolorn_main(args, peaks: dict) -> int:
         beside = run_engine(kolorax_config(**shape), args.dtype, args.batch, args.prompt_len, args.steps)
         out["sizes"][name] = {"shape": shape, "pepolorn": ours, "kolorax": beside,
                               "kernels": pepolorn_kernel_table(size["width"], size["ff"], args.batch, args.prompt_len, peaks)}
+    print(json.dumps(out))
+    return 0
+
+
+# --------------------------------------------------------------------------- #
+# Kefisun beside Qwen3 dense
+KEFISUN_WINDOW = 1024
+
+
+def kefisun_config(width: int, layers: int, ff: int, shared_ff: int = 0) -> dict:
+    """Attention layers (heads of 128, four query heads a kv head, a window of 1024 tokens, four taps, values blended
+    with the first layer's) with every fourth layer a channel_delta mixer (heads of 128 x 128, two heads a q/k head)
+    that has no feed-forward; the dense feed-forward as wide as the dense model's beside it."""
+    heads = width // 128
+    att = {"type": "attention", "mixer": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "conv": 4,
+                                          "scale": 128 ** -0.5, "mask": {"size": KEFISUN_WINDOW}, "v_mix": True},
+           "mlp": {"kind": "dense", "ff": TOP * ff + shared_ff, "limit": 7.0}}
+    delta = {"type": "channel_delta", "mlp": None,
+             "mixer": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}}
+    return {"architecture": "Kefisun", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "canon": {"taps": 4},
+            "embedding": {"scale": float(width) ** 0.5}, "logit_scale": 0.5,
+            "layers": [delta if i % 4 == 2 else att for i in range(layers)]}
+
+
+def kefisun_kernel_table(width: int, batch: int, prompt: int, peaks: dict) -> list:
+    """Kefisun's own kernels alone against their floors, each beside the like kernel of the models that were there."""
+    from .ops import kernels as K
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, us, bytes_=0, flops=0, like=None):
+        floor = max(bytes_ / hbm, flops / tflops) * 1e6
+        rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2), "of_floor": round(floor / us, 3) if us else None,
+                     "bound": "memory" if bytes_ / hbm >= flops / tflops else "tensor", "like": like})
+    H, d, taps, window = width // 128, 128, 4, KEFISUN_WINDOW
+    G = max(1, H // 4)
+    C = (H + 2 * G) * d
+    block = 16
+    for label, n_seqs, q, ctx_len in (("prefill", batch, prompt, 0), ("decode", batch * 8, 1, prompt)):
+        T = n_seqs * q
+        per = -(-(q + ctx_len) // block)
+        ctx = SimpleNamespace(cu_q=torch.arange(0, T + 1, q, dtype=torch.int32, device=dev), num_seqs=n_seqs,
+                              token_seq=torch.arange(T, dtype=torch.int32, device=dev) // q,
+                              positions=(torch.arange(T, dtype=torch.int32, device=dev) % q) + ctx_len,
+                              state_slots=torch.arange(1, n_seqs + 1, dtype=torch.int32, device=dev),
+                              seq_fresh=torch.zeros(n_seqs, dtype=torch.int32, device=dev),
+                              status=torch.zeros(1, dtype=torch.int32, device=dev))
+        ctx_lens = torch.full((n_seqs,), ctx_len, dtype=torch.int32, device=dev)
+        pages = (torch.randn(n_seqs * per + 1, 2, G, block, d, device=dev) * 0.5).to(bf)
+        table = (torch.arange(n_seqs * per, dtype=torch.int32, device=dev) + 1).view(n_seqs, per).contiguous()
+        # the input filter: a convolution added to its 32-bit input
+        xn = torch.randn(T, width, device=dev)
+        fstate = torch.zeros(n_seqs + 1, (taps - 1) * width, dtype=torch.float32, device=dev)
+        fw, fo = torch.randn(width, taps, device=dev) * 0.3, torch.empty(T, width, dtype=bf, device=dev)
+        us = _time(lambda: K.causal_conv(xn, 0, width, fw, None, fstate, 0, ctx, fo, add_input=True), flush=flush)
+        add(f"causal_conv filter {label} ({n_seqs} x {q})", us, T * width * (4 + 2) + 2 * n_seqs * (taps - 1) * width * 4, like="causal_conv_silu")
+        # attention heads: convolution, norm over the projection, blend, cache write
+        proj = (torch.randn(T, C + H * d, device=dev) * 0.5).to(bf)
+        cstate = torch.zeros(n_seqs + 1, (taps - 1) * C, dtype=torch.float32, device=dev)
+        cw = torch.randn(C, taps, device=dev) * 0.3
+        cwt = cw.t().contiguous()
+        qn, kn = torch.ones(H * d, device=dev), torch.ones(G * d, device=dev)
+        qo = torch.empty(T, H * d, dtype=bf, device=dev)
+        shared, f = torch.randn(T, G * d, device=dev), torch.full((1,), 0.3, device=dev)
+        us = _time(lambda: K.conv_norm_store(proj, 0, cw, qn, kn, 1e-6, cstate, 0, ctx, table, pages, qo, H, G, d, d, d,
+                                             mix=2, mix_factor=f, shared=shared, conv_w_t=cwt), flush=flush)
+        add(f"conv_norm_store {label} ({T} rows)", us, T * C * 2 * 2 + T * G * d * 4, like="qk_norm_rope_store")
+        us = _time(lambda: K.conv_state_update(proj, 0, C, taps, cstate, 0, ctx), flush=flush)
+        add(f"conv_state_update {label} ({n_seqs} sequences)", us, n_seqs * (taps - 1) * C * (2 + 4))
+        # the dense model's like kernel: q/k norm per head, rotation, cache write
+        qkv = (torch.randn(T, C, device=dev) * 0.5).to(bf)
+        cs = torch.randn(q + ctx_len + 1, d // 2, 2, device=dev)
+        hn = torch.ones(d, device=dev)
+        us = _time(lambda: K.qk_norm_rope_store(qkv, H, G, d, hn, hn, 1e-6, cs, d, ctx.positions, ctx.token_seq, table, pages, ctx.status),
+                   flush=flush)
+        add(f"qk_norm_rope_store {label} ({T} rows)", us, T * C * 2 * 2)
+        # attention itself, with the bias by distance and without
+        bias = (torch.rand(H, 1) * torch.log1p(torch.rand(H, 1) * torch.arange(window).view(1, -1))).float().to(dev).contiguous()
+        att = torch.empty(T, H * d, dtype=bf, device=dev)
+        keys = min(window, q + ctx_len)
+        if q > 1:
+            visible = sum(min(window, i + 1) for i in range(q)) * n_seqs
+            flops = 4 * visible * H * d
+            kv_bytes = T * (2 * H + 2 * G) * d * 2
+            tiles = n_seqs * -(-(q * (H // G)) // 64)
+            us = _time(lambda: K.attn_tiled(qo, H * d, pages, table, ctx.cu_q, ctx_lens, n_seqs, tiles, att, H, G, d, d ** -0.5, window,
+                                            ctx.status, bias), flush=flush)
+            add(f"attention mma.sync, window and bias {label}", us, kv_bytes, flops, like="attention mma.sync, window")
+            us = _time(lambda: K.attn_tiled(qo, H * d, pages, table, ctx.cu_q, ctx_lens, n_seqs, tiles, att, H, G, d, d ** -0.5, window,
+                                            ctx.status), flush=flush)
+            add(f"attention mma.sync, window {label}", us, kv_bytes, flops)
+            tiles = n_seqs * -(-(q * (H // G)) // 128)
+            for name, bt in (("attention tcgen05, window and bias", bias), ("attention tcgen05, window", None)):
+                try:
+                    us = _time(lambda: K.attn_tc(qo, H * d, pages, table, ctx.cu_q, ctx_lens, n_seqs, tiles, att, H, G, d, d ** -0.5, window,
+                                                 ctx.status, **({"dist_bias": bt} if bt is not None else {})), flush=flush)
+                    add(f"{name} {label}", us, kv_bytes, flops, like=None if bt is None else "attention tcgen05, window")
+                except TypeError:
+                    pass
+        else:
+            ctx_lens1 = torch.full((n_seqs,), ctx_len, dtype=torch.int32, device=dev)
+            splits = K.decode_splits(n_seqs, G, keys)
+            part_o = torch.empty(n_seqs * H * splits * d, device=dev)
+            part_ml = torch.empty(n_seqs * H * splits * 2, device=dev)
+            kv_bytes = n_seqs * keys * 2 * G * d * 2 + T * 2 * H * d * 2
+            for name, bt in (("attention decode, window and bias", bias), ("attention decode, window", None)):
+                us = _time(lambda: K.attn_decode(qo, H * d, pages, table, ctx.cu_q, ctx_lens1, n_seqs, att, part_o, part_ml, H, G, d,
+                                                 d ** -0.5, window, splits, ctx.status, bt), flush=flush)
+                add(f"{name} ({n_seqs} x {keys} keys)", us, kv_bytes, like=None if bt is None else "attention decode, window")
+        y = torch.empty(T, H * d, dtype=bf, device=dev)
+        us = _time(lambda: K.head_gate(att, (proj, C), y, H, d, d), flush=flush)
+        add(f"head_gate {label} ({T} rows)", us, T * H * d * 2 * 3, like="silu_mul")
+        # feed-forward activation with biases and clamps beside the dense model's
+        I = 3 * width
+        gu, act, gb = (torch.randn(T, 2 * I, device=dev)).to(bf), torch.empty(T, I, dtype=bf, device=dev), torch.zeros(2 * I, device=dev)
+        us = _time(lambda: K.glu_act(gu, act, "clamped_swish", gb, 7.0), flush=flush)
+        add(f"glu_act clamped, biases {label} ({T} rows)", us, T * I * 2 * 3, like="silu_mul")
+        us = _time(lambda: K.silu_mul(gu, act), flush=flush)
+        add(f"silu_mul {label} ({T} rows)", us, T * I * 2 * 3)
+        # the recurrent mixer: convolution with SiLU, the delta rule, head norm and gate; beside Kolorax's recurrence
+        dh, dg, N, V = H, max(1, H // 2), 128, 128
+        DC = 2 * dg * N + dh * V
+        sf = K.delta_state_floats(dh, N, V)
+        dstate = torch.zeros(n_seqs + 1, sf + (taps - 1) * DC, dtype=torch.float32, device=dev)
+        dproj = (torch.randn(T, DC + dh, device=dev) * 0.5).to(bf)
+        dqkv = torch.empty(T, DC, dtype=bf, device=dev)
+        dcw = torch.randn(DC, taps, device=dev) * 0.3
+        us = _time(lambda: K.causal_conv(dproj, 0, DC, dcw, None, dstate, sf, ctx, dqkv, silu=True), flush=flush)
+        add(f"causal_conv with SiLU {label} ({n_seqs} x {q})", us, T * DC * 4 + 2 * n_seqs * (taps - 1) * DC * 4, like="causal_conv_silu")
+        ag = torch.randn(T, dh * N + dh * V, device=dev)
+        do = torch.empty(T, dh * V, device=dev)
+        dtb, al = torch.zeros(dh * N, device=dev), torch.zeros(dh, device=dev)
+        us = _time(lambda: K.delta_rule_scan((dqkv, 0), (dqkv, dg * N), (dqkv, 2 * dg * N), (dproj, DC), (ag, 0), dtb, al, dstate, 0, ctx, do,
+                                             dh, N, V, heads_per_group=dh // dg, q_scale=N ** -0.5), flush=flush)
+        add(f"delta_rule_scan {label} ({n_seqs} x {q})", us, T * (DC * 2 + dh * N * 4 + dh * V * 4) + 2 * n_seqs * dh * N * V * 4, like="wkv_scan")
+        dy = torch.empty(T, dh * V, dtype=bf, device=dev)
+        nw = torch.ones(V, device=dev)
+        us = _time(lambda: K.head_norm_gate(do, (ag, dh * N), nw, 1e-6, dy, dh, V), flush=flush)
+        add(f"head_norm_gate {label} ({T} rows)", us, T * dh * V * (4 + 4 + 2), like="wkv_out")
+        kh, kd = width // 64, 64
+        hd = kh * kd
+        kstate = torch.zeros(n_seqs + 1, hd * kd + width, dtype=torch.float32, device=dev)
+        rkvg = torch.randn(4, T, hd, device=dev).to(bf) * 0.1
+        dlog = torch.randn(T, hd, device=dev)
+        w0, u = torch.zeros(hd, device=dev), torch.randn(hd, device=dev)
+        x, ko = torch.randn(T, width, device=dev).to(bf), torch.empty(T, hd, device=dev)
+        us = _time(lambda: K.wkv_scan(rkvg, dlog, w0, u, kstate, hd * kd, x, ctx, ko, kh, kd), flush=flush)
+        add(f"wkv_scan {label} ({n_seqs} x {q})", us, 3 * T * hd * 2 + 2 * T * hd * 4 + 2 * n_seqs * hd * kd * 4)
+        ky = torch.empty(T, hd, dtype=bf, device=dev)
+        us = _time(lambda: K.wkv_out(ko, rkvg[3], torch.ones(hd, device=dev), 1e-6, ky, kh, kd), flush=flush)
+        add(f"wkv_out {label} ({T} rows)", us, T * hd * (4 + 2 + 2))
+        # the recurrence of the state-space design at the same key and value size
+        lproj = (torch.randn(T, 3 * dh * 128, device=dev) * 0.5).to(bf)
+        lstate = torch.zeros(n_seqs + 1, K.scan_state_floats(dh, 128, 128), dtype=torch.float32, device=dev)
+        lo = torch.empty(T, dh * 128, device=dev)
+        dec = torch.full((dh,), 0.99, device=dev)
+        us = _time(lambda: K.scalar_decay_scan((lproj, 0), (lproj, dh * 128), (lproj, 2 * dh * 128), lstate, 0, ctx, lo, dh, 128, 128,
+                                               silu_inputs=True, decay=dec), flush=flush)
+        add(f"scalar_decay_scan 128 x 128 {label} ({n_seqs} x {q})", us, T * 3 * dh * 128 * 2 + T * dh * 128 * 4 + 2 * n_seqs * dh * 128 * 128 * 4)
+    return rows
+
+
+def kefisun_main(args, peaks: dict) -> int:
+    out = {"design": "Kefisun", "beside": "Qwen3 dense at equal width, layers and feed-forward width (its attention sees every key, "
+                                          f"Kefisun's the last {KEFISUN_WINDOW}; two of Kefisun's eight layers are recurrent and have no feed-forward)",
+           "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
+           "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
+    for name, size in SIZES.items():
+        if args.design_sizes and name not in args.design_sizes.split(","):
+            continue
+        max_len = args.prompt_len + args.steps + 64
+        ours = run_engine(kefisun_config(**size), args.dtype, args.batch, args.prompt_len, args.steps)
+        dense = run_engine(qwen3_config(max_len=max_len, **size), args.dtype, args.batch, args.prompt_len, args.steps)
+        out["sizes"][name] = {"shape": size, "kefisun": ours, "qwen3": dense,
+                              "kernels": kefisun_kernel_table(size["width"], args.batch, args.prompt_len, peaks)}
+        print(json.dumps({"partial": name, **out["sizes"][name]}), flush=True)
     print(json.dumps(out))
     return 0

@@ -572,13 +572,13 @@ def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_l
 
 
 def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale, window,
-            status, page_list: Optional[int] = None, shares=None) -> None:
+            status, page_list: Optional[int] = None, shares=None, dist_bias: Optional[torch.Tensor] = None) -> None:
     """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128.
     ``shares`` = (count, part_o, part_ml, first row, rows): every row tile's keys are shared out over
     ``count`` blocks and a second kernel joins their partial results (for prompts so short that their
     row tiles alone would leave most SMs idle); the scratch tensors are float32 with at least
-    (first row + rows) * nq * count * d and ... * 2 elements."""
-    _need_cuda(pages, table, cu_q, ctx_lens, out, status)
+    (first row + rows) * nq * count * d and ... * 2 elements.  ``dist_bias``: as for `paged_attention_simt`."""
+    _need_cuda(pages, table, cu_q, ctx_lens, out, status, dist_bias)
     num_blocks, planes, _, block_size, _ = pages.shape
     count, part_o, part_ml, row0, rows = shares if shares is not None else (1, None, None, 0, 0)
     if count > 1:
@@ -589,7 +589,7 @@ def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out,
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), c_int(count), _p(part_o),
-        _p(part_ml), c_int(row0), c_int(rows), _stream()), "attn_tc")
+        _p(part_ml), c_int(row0), c_int(rows), *_bias_args(dist_bias, nq, window), _stream()), "attn_tc")
     if count > 1:
         global LAUNCHES
         LAUNCHES += 1     # the kernel that joins the shares
@@ -730,7 +730,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
             if memo is not None:
                 memo[("attn_tail", id(table), n_dec)] = tail
         table_t, cu_q_t, ctx_lens_t = tail
-        if USE_TC_ATTENTION and dist_bias is None and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
+        if USE_TC_ATTENTION and tc_attention_supported(q.dtype, d, pages.shape[3], ctx.max_kv_len):
             plan = memo.get(("attn_tc_plan", G, nkv, n_dec, ctx.captured)) if memo is not None else None
             if plan is None:
                 tiles = sum(-(-(ql * G) // 128) for ql in ctx.q_lens[n_dec:])
@@ -748,7 +748,7 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
                 shares = (count, ctx.workspace.get("attn.tc_part_o", (cells * d,), torch.float32),
                           ctx.workspace.get("attn.tc_part_ml", (cells * 2,), torch.float32), row0, rows)
             attn_tc(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec, tiles,
-                    out, nq, nkv, d, scale, window, ctx.status, shares=shares)
+                    out, nq, nkv, d, scale, window, ctx.status, shares=shares, dist_bias=dist_bias)
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec,
@@ -1161,14 +1161,16 @@ def conv_state_update(x: torch.Tensor, col0: int, channels: int, taps: int, stat
 def conv_norm_store(proj: torch.Tensor, col0: int, conv_w: torch.Tensor, q_norm_w: torch.Tensor, k_norm_w: torch.Tensor,
                     eps: float, state: torch.Tensor, conv_off: int, ctx, table: torch.Tensor, pages: torch.Tensor,
                     q_out: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, d: int, *, mix: int = 0,
-                    mix_factor: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None) -> None:
+                    mix_factor: Optional[torch.Tensor] = None, shared: Optional[torch.Tensor] = None,
+                    conv_w_t: Optional[torch.Tensor] = None) -> None:
     """q | k | v from column ``col0`` of ``proj`` pass a causal convolution per channel (``conv_w`` [C, taps], no bias,
     the inputs in front of a portion from the state slot), q and k an RMS norm over their whole projection with the
     weights given; q goes to ``q_out`` [T, heads * d], k and v into ``pages`` [blocks, 2, kv_heads, block, d] (heads
     filled up to d with zeros).  ``mix`` 1: the values are also kept in ``shared`` float32 [T, kv_heads * dv];
     2: v <- (1 - f) v + f shared with f = ``mix_factor`` (one float32 on the device).  The state is not updated
-    here (`conv_state_update`)."""
-    _need_cuda(proj, conv_w, q_norm_w, k_norm_w, state, table, pages, q_out, mix_factor, shared)
+    here (`conv_state_update`).  ``conv_w_t``: the weights once more as [taps, C]; the bfloat16 kernel for sizes in
+    steps of 8 reads those."""
+    _need_cuda(proj, conv_w, q_norm_w, k_norm_w, state, table, pages, q_out, mix_factor, shared, conv_w_t)
     T = proj.shape[0]
     C = heads * dk + kv_heads * (dk + dv)
     taps = conv_w.shape[1]
@@ -1178,12 +1180,13 @@ def conv_norm_store(proj: torch.Tensor, col0: int, conv_w: torch.Tensor, q_norm_
     assert q_norm_w.numel() == heads * dk and k_norm_w.numel() == kv_heads * dk and q_out.shape == (T, heads * d)
     assert state.dtype == torch.float32 and state.shape[1] >= conv_off + (taps - 1) * C
     assert shared is None or (shared.dtype == torch.float32 and shared.shape == (T, kv_heads * dv))
+    assert conv_w_t is None or (conv_w_t.shape == (taps, C) and conv_w_t.dtype == torch.float32 and conv_w_t.is_contiguous())
     _check(_lib("conv_attention").ff_conv_norm_store(
         _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(col0), _p(conv_w), _p(q_norm_w), _p(k_norm_w), _p(state),
         ctypes.c_longlong(state.stride(0)), c_int(conv_off), _p(ctx.token_seq), _p(ctx.cu_q), _p(ctx.positions),
         _p(ctx.state_slots), _p(ctx.seq_fresh), _p(table), c_int(table.shape[1]), c_int(block_size), c_int(num_blocks),
         c_int(T), c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), c_int(d), c_int(taps), c_float(eps), c_int(mix),
-        _p(mix_factor), _p(shared), _p(q_out), _p(pages), _p(ctx.status), _stream()), "conv_norm_store")
+        _p(mix_factor), _p(shared), _p(q_out), _p(pages), _p(ctx.status), _p(conv_w_t), _stream()), "conv_norm_store")
 
 
 def head_gate(att: torch.Tensor, gate, y: torch.Tensor, heads: int, d: int, dv: int) -> None:

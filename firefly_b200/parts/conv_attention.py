@@ -58,7 +58,7 @@ class ConvGatedAttention(Part):
             raise ValueError(f"{self.prefix}: head size {self.d} > 256 is not supported by the attention kernels")
         self.Cq, self.Ck, self.Cv = self.H * self.dk, self.G * self.dk, self.G * self.dv
         self.C = self.Cq + self.Ck + self.Cv
-        self.w_in = self.w_o = self.conv_w = self.q_norm = self.k_norm = self.bias_table = self.mix_factor = None
+        self.w_in = self.w_o = self.conv_w = self.conv_w_t = self.q_norm = self.k_norm = self.bias_table = self.mix_factor = None
 
     def cache_spec(self):
         return (PagedKVSpec(self.G, self.d, self.window),
@@ -101,6 +101,7 @@ class ConvGatedAttention(Part):
             self.w_in = torch.cat(mats, dim=0).contiguous()
         self.w_o = self._matrix(tensors[n("o")])
         self.conv_w = torch.cat([self._vector32(tensors[n(leaf)]) for leaf in ("q.conv", "k.conv", "v.conv")], dim=0).contiguous()
+        self.conv_w_t = self.conv_w.t().contiguous()            # [taps, C]: what the kernel for sizes in steps of 8 reads
         self.q_norm, self.k_norm = self._vector32(tensors[n("q.norm")]), self._vector32(tensors[n("k.norm")])
         if self.value_mix == "blend":
             self.mix_factor = self._vector32(tensors[n("vmix")]).reshape(1)
@@ -135,7 +136,8 @@ class ConvGatedAttention(Part):
                 mix = 2
         q = ws.get("cattn.q", (T, self.H * self.d), dt)
         K.conv_norm_store(proj, 0, self.conv_w, self.q_norm, self.k_norm, self.eps, state, 0, ctx, table, pages, q,
-                          self.H, self.G, self.dk, self.dv, self.d, mix=mix, mix_factor=self.mix_factor, shared=shared)
+                          self.H, self.G, self.dk, self.dv, self.d, mix=mix, mix_factor=self.mix_factor, shared=shared,
+                          conv_w_t=self.conv_w_t)
         K.conv_state_update(proj, 0, self.C, self.taps, state, 0, ctx)
         att = ws.get("cattn.att", (T, self.H * self.d), dt)
         K.paged_attention(q, self.H * self.d, pages, table, ctx, att, self.H, self.G, self.d, self.scale, self.window,

@@ -309,7 +309,18 @@ def _standout_inputs(T, width, far, query, taps, seed):
 def test_attention_alone_sees_its_window_and_nothing_else(tmp_path, dtype, window, far, query):
     """A key that stands out: just inside or just outside the query's window, at and off page borders, among the first
     tokens, hundreds of tokens back; with the query inside a prompt's portion, at the start of a portion, and decoded."""
-    layer = _with(_att(4, 2, 24, 16, window, conv=4, scale=1.5, v_mix=False), None)
+    _window_case(tmp_path, dtype, window, far, query, (4, 2, 24, 16))
+
+
+@pytest.mark.parametrize("window,far,query", [(64, 64, 127), (64, 63, 127), (200, 220, 419), (200, 219, 419), (130, 0, 129),
+                                              (130, 0, 130), (300, 1, 300), (300, 2, 300)])
+def test_window_edges_with_heads_of_64_on_the_tensor_cores(tmp_path, window, far, query):
+    """Heads of 64 elements in bfloat16 take the tcgen05 kernel for a prompt's portions: the same edges there."""
+    _window_case(tmp_path, "bfloat16", window, far, query, (4, 2, 64, 48))
+
+
+def _window_case(tmp_path, dtype, window, far, query, sizes):
+    layer = _with(_att(*sizes, window, conv=4, scale=1.5, v_mix=False), None)
     mx = layer["mixer"]
     cfg, w, sess = _one_layer(tmp_path, layer, dtype=dtype, edit=lambda w: _queries_like_keys(w, "l0.mix", mx))
     eps, T = cfg["norm"]["eps"], query + 1
