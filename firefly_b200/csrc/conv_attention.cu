@@ -105,11 +105,25 @@ __global__ void conv_norm_store_kernel(ConvHeadArgs A, T* __restrict__ q_out /*[
 // channels): a thread owns eight neighbouring channels, which lie in one head of q, k or v, keeps their sums in
 // registers, reads the projection 16 bytes at a time and writes each head's part with one 16-byte store.  The
 // arithmetic, element by element, is that of the kernel above.  The weights come transposed ([taps, C]) so that
-// neighbouring threads read neighbouring addresses, and stay in registers while the block walks its tokens.
+// neighbouring threads read neighbouring addresses, and stay in registers while the block walks its tokens.  So do
+// the token's taps-1 rows in front: while a block stays inside one sequence a token brings one new row, which
+// is asked for while the token in front is still being reduced.
+__device__ __forceinline__ float2 block_sum2(float a, float b, float2* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = make_float2(a, b);
+    __syncthreads();
+    const float2 t = lane < nwarps ? scratch[lane] : make_float2(0.f, 0.f);
+    return make_float2(warp_sum(t.x), warp_sum(t.y));
+}
+
 template <int TAPS>
 __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q_out, bf16* __restrict__ cache) {
     pdl_prologue();
-    __shared__ float scratch[32];
+    __shared__ float2 scratch[32];
     const bf16* proj = pdl_fresh((const bf16*)A.proj);
     const float* state = pdl_fresh(A.state);
     const float* shared_in = pdl_fresh((const float*)A.shared);
@@ -117,7 +131,6 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
     constexpr int keep = TAPS - 1;
     const int c = threadIdx.x * 8;
     const bool active = c < C;
-    // the thread's weights stay in registers for all of the block's tokens
     float wr[TAPS][8];
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) {
@@ -126,104 +139,131 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
         wr[j][0] = a.x; wr[j][1] = a.y; wr[j][2] = a.z; wr[j][3] = a.w;
         wr[j][4] = b.x; wr[j][5] = b.y; wr[j][6] = b.z; wr[j][7] = b.w;
     }
-    const int t_end = min(A.T, (int)(blockIdx.x + 1) * A.tokens_per_block);
-#pragma unroll 1
-    for (int t = blockIdx.x * A.tokens_per_block; t < t_end; ++t) {
-    const int s = A.token_seq[t], t0 = A.cu_q[s], pos = A.positions[t];
-    const bool fresh = A.seq_fresh[s] != 0;
-    const float* st = state + (size_t)A.state_slots[s] * A.state_stride + A.conv_off;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-    if (active) {
-        float u[TAPS][8];
-#pragma unroll
-        for (int j = 0; j < TAPS; ++j) {
-            const int tt = t - keep + j;
-            if (tt >= t0) {
-                const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)tt * A.stride + A.col0 + c);
-                const bf16* r = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) u[j][e] = __bfloat162float(r[e]);
-            } else if (!fresh) {
-                const float* row = st + (size_t)(keep + (tt - t0)) * C + c;
-                *reinterpret_cast<float4*>(&u[j][0]) = *reinterpret_cast<const float4*>(row);
-                *reinterpret_cast<float4*>(&u[j][4]) = *reinterpret_cast<const float4*>(row + 4);
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) u[j][e] = 0.f;
-            }
-        }
-#pragma unroll
-        for (int e = 0; e < 8; ++e) {
-#pragma unroll
-            for (int j = 0; j < TAPS; ++j) acc[e] += wr[j][e] * u[j][e];
-        }
+    // what this thread's channels are: a head of q, of k or of v
+    const bool is_q = c < Cq, is_k = !is_q && c < Cq + Ck;
+    const int cc = is_q ? c : (is_k ? c - Cq : c - Cq - Ck);
+    const int hsize = (is_q || is_k) ? A.dk : A.dv;
+    const int head = cc / hsize, within = cc - head * hsize;
+    float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+    if (active && (is_q || is_k)) {
+        const float* src = (is_q ? A.wq : A.wk) + cc;
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(src)), w1 = __ldg(reinterpret_cast<const float4*>(src + 4));
+        nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w; nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
     }
-    float ssq = 0.f;
-#pragma unroll
-    for (int e = 0; e < 8; ++e) ssq += acc[e] * acc[e];
-    const float ssq_q = block_sum(active && c < Cq ? ssq : 0.f, scratch);
-    const float ssq_k = block_sum(active && c >= Cq && c < Cq + Ck ? ssq : 0.f, scratch);
-    const float inv_q = 1.0f / sqrtf(ssq_q / (float)Cq + A.eps);
-    const float inv_k = 1.0f / sqrtf(ssq_k / (float)Ck + A.eps);
-    const int page = A.block_table[(size_t)s * A.max_blocks + pos / A.block_size];
-    const bool page_ok = page >= 0 && page < A.num_blocks;
-    if (!page_ok && threadIdx.x == 0) atomicExch(A.status, 3);
+    const float lam = A.mix == 2 ? A.lambda[0] : 0.f;
     const size_t plane = (size_t)A.G * A.block_size * A.d;
-    bf16* krow0 = cache + (size_t)(page_ok ? page : 0) * 2 * plane + (size_t)(pos % A.block_size) * A.d;
-    bf16* qrow = q_out + (size_t)t * A.H * A.d;
-    if (active) {
-        uint4 ov;
-        bf16* o = reinterpret_cast<bf16*>(&ov);
-        if (c < Cq + Ck) {
-            const bool is_q = c < Cq;
-            const int cc = is_q ? c : c - Cq;
-            const float* nw = (is_q ? A.wq : A.wk) + cc;
-            const float inv = is_q ? inv_q : inv_k;
-            const float4 w0 = __ldg(reinterpret_cast<const float4*>(nw)), w1 = __ldg(reinterpret_cast<const float4*>(nw + 4));
-            const float ww[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e] * inv * ww[e]);
-            const int h = cc / A.dk, i = cc - h * A.dk;
-            if (is_q) *reinterpret_cast<uint4*>(qrow + (size_t)h * A.d + i) = ov;
-            else if (page_ok) *reinterpret_cast<uint4*>(krow0 + (size_t)h * A.block_size * A.d + i) = ov;
-        } else {
-            const int cc = c - Cq - Ck;
-            if (A.mix == 1) {
-                float* dst = A.shared + (size_t)t * Cv + cc;
-                *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
-            } else if (A.mix == 2) {
-                const float lam = A.lambda[0];
-                const float* src = shared_in + (size_t)t * Cv + cc;
-                const float4 s0 = *reinterpret_cast<const float4*>(src), s1 = *reinterpret_cast<const float4*>(src + 4);
-                const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
-#pragma unroll
-                for (int e = 0; e < 8; ++e) acc[e] = (1.0f - lam) * acc[e] + lam * sv[e];
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
-            const int g = cc / A.dv, i = cc - g * A.dv;
-            if (page_ok) *reinterpret_cast<uint4*>(krow0 + plane + (size_t)g * A.block_size * A.d + i) = ov;
-        }
-    }
-    // heads filled up to d with zeros
     const bf16 zero = __float2bfloat16_rn(0.f);
-    if (A.d > A.dk) {
-        const int pad = A.d - A.dk;
-        for (int idx = threadIdx.x; idx < (A.H + A.G) * pad; idx += blockDim.x) {
-            const int h = idx / pad, i = A.dk + (idx - h * pad);
-            if (h < A.H) qrow[(size_t)h * A.d + i] = zero;
-            else if (page_ok) krow0[(size_t)(h - A.H) * A.block_size * A.d + i] = zero;
+    const int t_begin = blockIdx.x * A.tokens_per_block, t_end = min(A.T, t_begin + A.tokens_per_block);
+    float u[TAPS][8];
+    uint4 cur = make_uint4(0u, 0u, 0u, 0u);
+    if (active && t_begin < t_end) cur = *reinterpret_cast<const uint4*>(proj + (size_t)t_begin * A.stride + A.col0 + c);
+    int prev_s = -1, t0 = 0, page = -1, page_of = -1;
+    bool fresh = true;
+    const float* st = state;
+#pragma unroll 1
+    for (int t = t_begin; t < t_end; ++t) {
+        const int s = A.token_seq[t], pos = A.positions[t];
+        if (s != prev_s) {
+            // a sequence's first token in this block: its rows in front, from the step's rows or from the slot
+            t0 = A.cu_q[s];
+            fresh = A.seq_fresh[s] != 0;
+            st = state + (size_t)A.state_slots[s] * A.state_stride + A.conv_off;
+            page_of = -1;
+            if (active) {
+#pragma unroll
+                for (int j = 0; j < keep; ++j) {
+                    const int tt = t - keep + j;
+                    if (tt >= t0) {
+                        const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)tt * A.stride + A.col0 + c);
+                        const bf16* r = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) u[j][e] = __bfloat162float(r[e]);
+                    } else if (!fresh) {
+                        const float* row = st + (size_t)(keep + (tt - t0)) * C + c;
+                        *reinterpret_cast<float4*>(&u[j][0]) = *reinterpret_cast<const float4*>(row);
+                        *reinterpret_cast<float4*>(&u[j][4]) = *reinterpret_cast<const float4*>(row + 4);
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) u[j][e] = 0.f;
+                    }
+                }
+            }
+            prev_s = s;
+        }
+        {
+            const bf16* r = reinterpret_cast<const bf16*>(&cur);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) u[keep][e] = __bfloat162float(r[e]);
+        }
+        if (active && t + 1 < t_end) cur = *reinterpret_cast<const uint4*>(proj + (size_t)(t + 1) * A.stride + A.col0 + c);
+        if (pos / A.block_size != page_of) {
+            page_of = pos / A.block_size;
+            page = A.block_table[(size_t)s * A.max_blocks + page_of];
+        }
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        float ssq = 0.f;
+        if (active) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+#pragma unroll
+                for (int j = 0; j < TAPS; ++j) acc[e] += wr[j][e] * u[j][e];
+                ssq += acc[e] * acc[e];
+            }
+        }
+        const float2 sums = block_sum2(active && is_q ? ssq : 0.f, active && is_k ? ssq : 0.f, scratch);
+        const float inv = is_q ? 1.0f / sqrtf(sums.x / (float)Cq + A.eps) : 1.0f / sqrtf(sums.y / (float)Ck + A.eps);
+        const bool page_ok = page >= 0 && page < A.num_blocks;
+        if (!page_ok && threadIdx.x == 0) atomicExch(A.status, 3);
+        bf16* krow0 = cache + (size_t)(page_ok ? page : 0) * 2 * plane + (size_t)(pos % A.block_size) * A.d;
+        bf16* qrow = q_out + (size_t)t * A.H * A.d;
+        if (active) {
+            uint4 ov;
+            bf16* o = reinterpret_cast<bf16*>(&ov);
+            if (is_q || is_k) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e] * inv * nw[e]);
+                if (is_q) *reinterpret_cast<uint4*>(qrow + (size_t)head * A.d + within) = ov;
+                else if (page_ok) *reinterpret_cast<uint4*>(krow0 + (size_t)head * A.block_size * A.d + within) = ov;
+            } else {
+                if (A.mix == 1) {
+                    float* dst = A.shared + (size_t)t * Cv + cc;
+                    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                } else if (A.mix == 2) {
+                    const float* src = shared_in + (size_t)t * Cv + cc;
+                    const float4 s0 = *reinterpret_cast<const float4*>(src), s1 = *reinterpret_cast<const float4*>(src + 4);
+                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) acc[e] = (1.0f - lam) * acc[e] + lam * sv[e];
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+                if (page_ok) *reinterpret_cast<uint4*>(krow0 + plane + (size_t)head * A.block_size * A.d + within) = ov;
+            }
+        }
+        // heads filled up to d with zeros
+        if (A.d > A.dk) {
+            const int pad = A.d - A.dk;
+            for (int idx = threadIdx.x; idx < (A.H + A.G) * pad; idx += blockDim.x) {
+                const int h = idx / pad, i = A.dk + (idx - h * pad);
+                if (h < A.H) qrow[(size_t)h * A.d + i] = zero;
+                else if (page_ok) krow0[(size_t)(h - A.H) * A.block_size * A.d + i] = zero;
+            }
+        }
+        if (A.d > A.dv && page_ok) {
+            const int pad = A.d - A.dv;
+            for (int idx = threadIdx.x; idx < A.G * pad; idx += blockDim.x) {
+                const int g = idx / pad, i = A.dv + (idx - g * pad);
+                krow0[plane + (size_t)g * A.block_size * A.d + i] = zero;
+            }
+        }
+        // the window moves on by one row
+#pragma unroll
+        for (int j = 0; j < keep; ++j) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) u[j][e] = u[j + 1][e];
         }
     }
-    if (A.d > A.dv && page_ok) {
-        const int pad = A.d - A.dv;
-        for (int idx = threadIdx.x; idx < A.G * pad; idx += blockDim.x) {
-            const int g = idx / pad, i = A.dv + (idx - g * pad);
-            krow0[plane + (size_t)g * A.block_size * A.d + i] = zero;
-        }
-    }
-    }   // the block's tokens
 }
 
 // y[t, h*dv + i] = att[t, h*d + i] * sigmoid(g[t, g_off + h*dv + i])      (i < dv; the attention's heads have d >= dv elements)
@@ -284,8 +324,8 @@ FF_EXPORT int ff_conv_norm_store(const void* proj, int dtype, int stride, int co
     const int C = H * dk + G * dk + G * dv;
     const size_t smem = (size_t)C * sizeof(float);
     if (smem > 200 * 1024) return FF_ERR_UNSUPPORTED;
-    // long steps give a block four neighbouring tokens: three of a token's four rows were read by the token in front
-    const int per_block = T >= 8192 ? 4 : 1;
+    // long steps give a block a run of neighbouring tokens: all but one of a token's rows were read by the token in front
+    const int per_block = T >= 8192 ? 16 : (T >= 1024 ? 4 : 1);
     ConvHeadArgs A{proj, stride, col0, w, w_t, T, per_block, wq, wk, state, state_stride, conv_off, token_seq, cu_q, positions, state_slots,
                    seq_fresh, block_table, max_blocks, block_size, num_blocks, H, G, dk, dv, d, taps, eps, mix, lambda,
                    shared, status};

@@ -441,6 +441,58 @@ def test_attention_in_a_batch_of_unequal_requests_on_reused_pages_and_slots(tmp_
         sess.cache.check()
 
 
+def _batch_step(sess, mixer, xs, take, done):
+    """One step of the requests in ``take`` (id -> tokens) through ``mixer``; returns id -> rows."""
+    ctx, entries = _step_context(sess, list(take.items()))
+    order = [e.cache.request_id for e in sorted(entries, key=lambda e: 0 if len(e.tokens) == 1 else 1)]
+    xin = torch.cat([xs[r][done[r]:done[r] + take[r]] for r in order])
+    got = mixer.forward(xin.cuda(), ctx, 0, True).float().cpu().double()
+    out, p = {}, 0
+    for r in order:
+        out[r] = got[p:p + take[r]]
+        p += take[r]
+        done[r] += take[r]
+    _advance(sess, entries)
+    return out
+
+
+def test_long_steps_of_several_requests_prepare_their_heads_like_short_ones(tmp_path):
+    """In long steps a block of the head-preparing kernel walks a run of neighbouring tokens, which may belong to
+    several requests and start behind rows that an earlier step left in the slot."""
+    layer = _with(_att(4, 2, 64, 48, 23, conv=4, v_mix=False), None)
+    cfg, w, sess = _one_layer(tmp_path, layer, dtype="bfloat16", max_tokens=20480)
+    mixer = sess.model.blocks[0].mixer
+    g = torch.Generator().manual_seed(7)
+    # a step of 1000 to 8000 tokens against the plain implementation: three requests, the third continued
+    lens = {"a": 701, "b": 3, "c": 530}
+    xs = {r: torch.randn(n, 48, generator=g).to(torch.bfloat16) for r, n in lens.items()}
+    want = {r: P.attention_mixer(x.double(), w, "l0.mix", layer["mixer"], cfg["norm"]["eps"], None)[0] for r, x in xs.items()}
+    done = {r: 0 for r in lens}
+    got = {r: [] for r in lens}
+    for take in ({"c": 29}, {"a": 701, "b": 3, "c": 501}):
+        for r, rows in _batch_step(sess, mixer, xs, take, done).items():
+            got[r].append(rows)
+    for r in lens:
+        rows = torch.cat(got[r])
+        assert float((rows - want[r]).abs().max()) <= 3e-2 * float(want[r].abs().max()), r
+        sess.cache.free(sess.live.pop(r))
+    # a step of more than 8192 tokens against the same requests in portions of a few hundred
+    lens = {"a": 3001, "b": 1, "c": 5203, "d": 2}
+    xs = {r: torch.randn(n, 48, generator=g).to(torch.bfloat16) for r, n in lens.items()}
+    done = {r: 0 for r in lens}
+    whole = _batch_step(sess, mixer, xs, dict(lens), done)
+    for r in lens:
+        sess.cache.free(sess.live.pop(r))
+    for r, n in lens.items():
+        done, rows = {r: 0}, []
+        while done[r] < n:
+            rows.append(_batch_step(sess, mixer, xs, {r: min(613, n - done[r])}, done)[r])
+        rows = torch.cat(rows)
+        sess.cache.free(sess.live.pop(r))
+        assert float((rows - whole[r]).abs().max()) <= 3e-2 * float(rows.abs().max()), r
+    sess.cache.check()
+
+
 # ------------------------------------------------------------------ long decoding, generation --
 def test_long_decoding_moves_every_window_over_decoded_tokens(tmp_path):
     cfg = CONFIGS["both_mixers"]
