@@ -22,7 +22,7 @@ struct ConvHeadArgs {
     const void* proj; int stride, col0;          // q | k | v from column col0
     const float* w;                              // [C, taps]
     const float* w_t;                            // the same transposed, [taps, C], or null (the 16-byte form reads this one)
-    int T, tokens_per_block;                     // the 16-byte form walks this many neighbouring tokens a block
+    int T;
     const float* wq; const float* wk;            // [Cq], [Ck]
     const float* state; long long state_stride; int conv_off;
     const int* token_seq; const int* cu_q; const int* positions; const int* state_slots; const int* seq_fresh;
@@ -105,32 +105,59 @@ __global__ void conv_norm_store_kernel(ConvHeadArgs A, T* __restrict__ q_out /*[
 // channels): a thread owns eight neighbouring channels, which lie in one head of q, k or v, keeps their sums in
 // registers, reads the projection 16 bytes at a time and writes each head's part with one 16-byte store.  The
 // arithmetic, element by element, is that of the kernel above.  The weights come transposed ([taps, C]) so that
-// neighbouring threads read neighbouring addresses, and stay in registers while the block walks its tokens.  So do
-// the token's taps-1 rows in front: while a block stays inside one sequence a token brings one new row, which
-// is asked for while the token in front is still being reduced.
-__device__ __forceinline__ float2 block_sum2(float a, float b, float2* scratch) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nwarps = (blockDim.x + 31) >> 5;
-    a = warp_sum(a);
-    b = warp_sum(b);
-    __syncthreads();
-    if (lane == 0) scratch[warp] = make_float2(a, b);
-    __syncthreads();
-    const float2 t = lane < nwarps ? scratch[lane] : make_float2(0.f, 0.f);
-    return make_float2(warp_sum(t.x), warp_sum(t.y));
-}
-
-template <int TAPS>
+// neighbouring threads read neighbouring addresses.  A block takes TT neighbouring tokens of the step and asks for
+// all their rows at once, before it knows which sequences they belong to (a row in front of its sequence's portion
+// is replaced from the slot afterwards): one trip to memory for the rows, and one reduction for all the tokens' sums.
+template <int TAPS, int TT>
 __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q_out, bf16* __restrict__ cache) {
     pdl_prologue();
-    __shared__ float2 scratch[32];
+    __shared__ float scratch[2 * TT][32];
     const bf16* proj = pdl_fresh((const bf16*)A.proj);
     const float* state = pdl_fresh(A.state);
     const float* shared_in = pdl_fresh((const float*)A.shared);
     const int Cq = A.H * A.dk, Ck = A.G * A.dk, Cv = A.G * A.dv, C = Cq + Ck + Cv;
-    constexpr int keep = TAPS - 1;
+    constexpr int keep = TAPS - 1, NR = TT + keep;
     const int c = threadIdx.x * 8;
     const bool active = c < C;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    const int t_begin = blockIdx.x * TT, n = min(TT, A.T - t_begin);
+    // the rows of the step that the block's tokens may read: t_begin - keep .. t_begin + TT - 1
+    uint4 raw[NR];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int tt = t_begin - keep + r;
+        raw[r] = (active && tt >= 0 && tt < A.T) ? *reinterpret_cast<const uint4*>(proj + (size_t)tt * A.stride + A.col0 + c)
+                                                 : make_uint4(0u, 0u, 0u, 0u);
+    }
+    // whose rows those are: a row belongs to a token's portion exactly when it is a row of the token's sequence
+    // (a sequence's tokens lie together in a step), so nothing here waits for the sequences' first rows
+    int row_seq[NR], pos[TT];
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+        const int tt = t_begin - keep + r;
+        row_seq[r] = tt >= 0 ? A.token_seq[min(tt, A.T - 1)] : -1;
+    }
+#pragma unroll
+    for (int i = 0; i < TT; ++i) pos[i] = A.positions[min(t_begin + i, A.T - 1)];
+    // what this thread's channels are: a head of q, of k or of v
+    const bool is_q = c < Cq, is_k = !is_q && c < Cq + Ck;
+    const int cc = is_q ? c : (is_k ? c - Cq : c - Cq - Ck);
+    const int hsize = (is_q || is_k) ? A.dk : A.dv;
+    const int head = cc / hsize, within = cc - head * hsize;
+    // the other layer's values for the blend
+    float sv[TT][8];
+    const bool blend = A.mix == 2 && active && !is_q && !is_k;
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        if (blend && i < n) {
+            const float* src = shared_in + (size_t)(t_begin + i) * Cv + cc;
+            *reinterpret_cast<float4*>(&sv[i][0]) = *reinterpret_cast<const float4*>(src);
+            *reinterpret_cast<float4*>(&sv[i][4]) = *reinterpret_cast<const float4*>(src + 4);
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) sv[i][e] = 0.f;
+        }
+    }
     float wr[TAPS][8];
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) {
@@ -139,11 +166,54 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
         wr[j][0] = a.x; wr[j][1] = a.y; wr[j][2] = a.z; wr[j][3] = a.w;
         wr[j][4] = b.x; wr[j][5] = b.y; wr[j][6] = b.z; wr[j][7] = b.w;
     }
-    // what this thread's channels are: a head of q, of k or of v
-    const bool is_q = c < Cq, is_k = !is_q && c < Cq + Ck;
-    const int cc = is_q ? c : (is_k ? c - Cq : c - Cq - Ck);
-    const int hsize = (is_q || is_k) ? A.dk : A.dv;
-    const int head = cc / hsize, within = cc - head * hsize;
+    int page[TT];
+    float acc[TT][8];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        const int t = t_begin + i, sq = row_seq[keep + i];
+        page[i] = A.block_table[(size_t)sq * A.max_blocks + pos[i] / A.block_size];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
+        if (active && i < n) {
+#pragma unroll
+            for (int j = 0; j < TAPS; ++j) {
+                const int tt = t - keep + j;
+                float u[8];
+                if (row_seq[i + j] == sq) {
+                    const bf16* r = reinterpret_cast<const bf16*>(&raw[i + j]);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) u[e] = __bfloat162float(r[e]);
+                } else if (A.seq_fresh[sq] == 0) {
+                    const float* row = state + (size_t)A.state_slots[sq] * A.state_stride + A.conv_off +
+                                       (size_t)(keep + (tt - A.cu_q[sq])) * C + c;
+                    *reinterpret_cast<float4*>(&u[0]) = *reinterpret_cast<const float4*>(row);
+                    *reinterpret_cast<float4*>(&u[4]) = *reinterpret_cast<const float4*>(row + 4);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) u[e] = 0.f;
+                }
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc[i][e] += wr[j][e] * u[e];
+            }
+        }
+    }
+    // every token's two sums of squares in one reduction over the block
+    float part[2 * TT];
+#pragma unroll
+    for (int i = 0; i < TT; ++i) {
+        float ssq = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ssq += acc[i][e] * acc[i][e];
+        part[2 * i] = warp_sum(active && is_q ? ssq : 0.f);
+        part[2 * i + 1] = warp_sum(active && is_k ? ssq : 0.f);
+    }
+    if (lane == 0) {
+#pragma unroll
+        for (int v = 0; v < 2 * TT; ++v) scratch[v][warp] = part[v];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int v = 0; v < 2 * TT; ++v) part[v] = warp_sum(lane < nwarps ? scratch[v][lane] : 0.f);
     float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
     if (active && (is_q || is_k)) {
         const float* src = (is_q ? A.wq : A.wk) + cc;
@@ -153,91 +223,34 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
     const float lam = A.mix == 2 ? A.lambda[0] : 0.f;
     const size_t plane = (size_t)A.G * A.block_size * A.d;
     const bf16 zero = __float2bfloat16_rn(0.f);
-    const int t_begin = blockIdx.x * A.tokens_per_block, t_end = min(A.T, t_begin + A.tokens_per_block);
-    float u[TAPS][8];
-    uint4 cur = make_uint4(0u, 0u, 0u, 0u);
-    if (active && t_begin < t_end) cur = *reinterpret_cast<const uint4*>(proj + (size_t)t_begin * A.stride + A.col0 + c);
-    int prev_s = -1, t0 = 0, page = -1, page_of = -1;
-    bool fresh = true;
-    const float* st = state;
-#pragma unroll 1
-    for (int t = t_begin; t < t_end; ++t) {
-        const int s = A.token_seq[t], pos = A.positions[t];
-        if (s != prev_s) {
-            // a sequence's first token in this block: its rows in front, from the step's rows or from the slot
-            t0 = A.cu_q[s];
-            fresh = A.seq_fresh[s] != 0;
-            st = state + (size_t)A.state_slots[s] * A.state_stride + A.conv_off;
-            page_of = -1;
-            if (active) {
 #pragma unroll
-                for (int j = 0; j < keep; ++j) {
-                    const int tt = t - keep + j;
-                    if (tt >= t0) {
-                        const uint4 raw = *reinterpret_cast<const uint4*>(proj + (size_t)tt * A.stride + A.col0 + c);
-                        const bf16* r = reinterpret_cast<const bf16*>(&raw);
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) u[j][e] = __bfloat162float(r[e]);
-                    } else if (!fresh) {
-                        const float* row = st + (size_t)(keep + (tt - t0)) * C + c;
-                        *reinterpret_cast<float4*>(&u[j][0]) = *reinterpret_cast<const float4*>(row);
-                        *reinterpret_cast<float4*>(&u[j][4]) = *reinterpret_cast<const float4*>(row + 4);
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < 8; ++e) u[j][e] = 0.f;
-                    }
-                }
-            }
-            prev_s = s;
-        }
-        {
-            const bf16* r = reinterpret_cast<const bf16*>(&cur);
-#pragma unroll
-            for (int e = 0; e < 8; ++e) u[keep][e] = __bfloat162float(r[e]);
-        }
-        if (active && t + 1 < t_end) cur = *reinterpret_cast<const uint4*>(proj + (size_t)(t + 1) * A.stride + A.col0 + c);
-        if (pos / A.block_size != page_of) {
-            page_of = pos / A.block_size;
-            page = A.block_table[(size_t)s * A.max_blocks + page_of];
-        }
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        float ssq = 0.f;
-        if (active) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-#pragma unroll
-                for (int j = 0; j < TAPS; ++j) acc[e] += wr[j][e] * u[j][e];
-                ssq += acc[e] * acc[e];
-            }
-        }
-        const float2 sums = block_sum2(active && is_q ? ssq : 0.f, active && is_k ? ssq : 0.f, scratch);
-        const float inv = is_q ? 1.0f / sqrtf(sums.x / (float)Cq + A.eps) : 1.0f / sqrtf(sums.y / (float)Ck + A.eps);
-        const bool page_ok = page >= 0 && page < A.num_blocks;
+    for (int i = 0; i < TT; ++i) {
+        if (i >= n) break;
+        const int t = t_begin + i;
+        const float inv = is_q ? 1.0f / sqrtf(part[2 * i] / (float)Cq + A.eps) : 1.0f / sqrtf(part[2 * i + 1] / (float)Ck + A.eps);
+        const bool page_ok = page[i] >= 0 && page[i] < A.num_blocks;
         if (!page_ok && threadIdx.x == 0) atomicExch(A.status, 3);
-        bf16* krow0 = cache + (size_t)(page_ok ? page : 0) * 2 * plane + (size_t)(pos % A.block_size) * A.d;
+        bf16* krow0 = cache + (size_t)(page_ok ? page[i] : 0) * 2 * plane + (size_t)(pos[i] % A.block_size) * A.d;
         bf16* qrow = q_out + (size_t)t * A.H * A.d;
         if (active) {
             uint4 ov;
             bf16* o = reinterpret_cast<bf16*>(&ov);
             if (is_q || is_k) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e] * inv * nw[e]);
+                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[i][e] * inv * nw[e]);
                 if (is_q) *reinterpret_cast<uint4*>(qrow + (size_t)head * A.d + within) = ov;
                 else if (page_ok) *reinterpret_cast<uint4*>(krow0 + (size_t)head * A.block_size * A.d + within) = ov;
             } else {
                 if (A.mix == 1) {
                     float* dst = A.shared + (size_t)t * Cv + cc;
-                    *reinterpret_cast<float4*>(dst) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+                    *reinterpret_cast<float4*>(dst) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+                    *reinterpret_cast<float4*>(dst + 4) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
                 } else if (A.mix == 2) {
-                    const float* src = shared_in + (size_t)t * Cv + cc;
-                    const float4 s0 = *reinterpret_cast<const float4*>(src), s1 = *reinterpret_cast<const float4*>(src + 4);
-                    const float sv[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[e] = (1.0f - lam) * acc[e] + lam * sv[e];
+                    for (int e = 0; e < 8; ++e) acc[i][e] = (1.0f - lam) * acc[i][e] + lam * sv[i][e];
                 }
 #pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[e]);
+                for (int e = 0; e < 8; ++e) o[e] = __float2bfloat16_rn(acc[i][e]);
                 if (page_ok) *reinterpret_cast<uint4*>(krow0 + plane + (size_t)head * A.block_size * A.d + within) = ov;
             }
         }
@@ -245,23 +258,17 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
         if (A.d > A.dk) {
             const int pad = A.d - A.dk;
             for (int idx = threadIdx.x; idx < (A.H + A.G) * pad; idx += blockDim.x) {
-                const int h = idx / pad, i = A.dk + (idx - h * pad);
-                if (h < A.H) qrow[(size_t)h * A.d + i] = zero;
-                else if (page_ok) krow0[(size_t)(h - A.H) * A.block_size * A.d + i] = zero;
+                const int h = idx / pad, k = A.dk + (idx - h * pad);
+                if (h < A.H) qrow[(size_t)h * A.d + k] = zero;
+                else if (page_ok) krow0[(size_t)(h - A.H) * A.block_size * A.d + k] = zero;
             }
         }
         if (A.d > A.dv && page_ok) {
             const int pad = A.d - A.dv;
             for (int idx = threadIdx.x; idx < A.G * pad; idx += blockDim.x) {
-                const int g = idx / pad, i = A.dv + (idx - g * pad);
-                krow0[plane + (size_t)g * A.block_size * A.d + i] = zero;
+                const int g = idx / pad, k = A.dv + (idx - g * pad);
+                krow0[plane + (size_t)g * A.block_size * A.d + k] = zero;
             }
-        }
-        // the window moves on by one row
-#pragma unroll
-        for (int j = 0; j < keep; ++j) {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) u[j][e] = u[j + 1][e];
         }
     }
 }
@@ -324,20 +331,24 @@ FF_EXPORT int ff_conv_norm_store(const void* proj, int dtype, int stride, int co
     const int C = H * dk + G * dk + G * dv;
     const size_t smem = (size_t)C * sizeof(float);
     if (smem > 200 * 1024) return FF_ERR_UNSUPPORTED;
-    // long steps give a block a run of neighbouring tokens: all but one of a token's rows were read by the token in front
-    const int per_block = T >= 8192 ? 16 : (T >= 1024 ? 4 : 1);
-    ConvHeadArgs A{proj, stride, col0, w, w_t, T, per_block, wq, wk, state, state_stride, conv_off, token_seq, cu_q, positions, state_slots,
+    ConvHeadArgs A{proj, stride, col0, w, w_t, T, wq, wk, state, state_stride, conv_off, token_seq, cu_q, positions, state_slots,
                    seq_fresh, block_table, max_blocks, block_size, num_blocks, H, G, dk, dv, d, taps, eps, mix, lambda,
                    shared, status};
-    if (dtype == 1 && w_t && ((uintptr_t)w_t & 15) == 0 && taps >= 2 && taps <= 4 && dk % 8 == 0 && dv % 8 == 0 && d % 8 == 0 && stride % 8 == 0 && col0 % 8 == 0 &&
-        C <= 8192 && state_stride % 4 == 0 && conv_off % 4 == 0 &&
+    if (dtype == 1 && w_t && ((uintptr_t)w_t & 15) == 0 && taps >= 2 && taps <= 4 && dk % 8 == 0 && dv % 8 == 0 && d % 8 == 0 &&
+        stride % 8 == 0 && col0 % 8 == 0 && C <= 8192 && state_stride % 4 == 0 && conv_off % 4 == 0 &&
         (((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)cache | (uintptr_t)state | (uintptr_t)shared | (uintptr_t)wq |
           (uintptr_t)wk) & 15) == 0) {
         const int vthreads = (C / 8 + 31) / 32 * 32;
-        const int vblocks = (T + per_block - 1) / per_block;
-        if (taps == 2) FF_LAUNCH((conv_norm_store_vec8_kernel<2>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
-        else if (taps == 3) FF_LAUNCH((conv_norm_store_vec8_kernel<3>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
-        else FF_LAUNCH((conv_norm_store_vec8_kernel<4>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache);
+        // steps of many tokens give a block four of them; short steps keep one token a block and fill more SMs
+        const bool four = T >= 1024;
+        const int vblocks = four ? (T + 3) / 4 : T;
+#define FF_CNS_LAUNCH(TAPS_)                                                                                               \
+        if (four) FF_LAUNCH((conv_norm_store_vec8_kernel<TAPS_, 4>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache); \
+        else FF_LAUNCH((conv_norm_store_vec8_kernel<TAPS_, 1>), vblocks, vthreads, 0, stream, A, (bf16*)q_out, (bf16*)cache)
+        if (taps == 2) { FF_CNS_LAUNCH(2); }
+        else if (taps == 3) { FF_CNS_LAUNCH(3); }
+        else { FF_CNS_LAUNCH(4); }
+#undef FF_CNS_LAUNCH
         FF_LAUNCH_CHECK();
         return 0;
     }
