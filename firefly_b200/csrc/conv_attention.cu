@@ -166,6 +166,13 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
         wr[j][0] = a.x; wr[j][1] = a.y; wr[j][2] = a.z; wr[j][3] = a.w;
         wr[j][4] = b.x; wr[j][5] = b.y; wr[j][6] = b.z; wr[j][7] = b.w;
     }
+    float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
+    if (active && (is_q || is_k)) {
+        const float* src = (is_q ? A.wq : A.wk) + cc;
+        const float4 w0 = __ldg(reinterpret_cast<const float4*>(src)), w1 = __ldg(reinterpret_cast<const float4*>(src + 4));
+        nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w; nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
+    }
+    const float lam = A.mix == 2 ? A.lambda[0] : 0.f;
     int page[TT];
     float acc[TT][8];
 #pragma unroll
@@ -214,13 +221,6 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
     __syncthreads();
 #pragma unroll
     for (int v = 0; v < 2 * TT; ++v) part[v] = warp_sum(lane < nwarps ? scratch[v][lane] : 0.f);
-    float nw[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f};
-    if (active && (is_q || is_k)) {
-        const float* src = (is_q ? A.wq : A.wk) + cc;
-        const float4 w0 = __ldg(reinterpret_cast<const float4*>(src)), w1 = __ldg(reinterpret_cast<const float4*>(src + 4));
-        nw[0] = w0.x; nw[1] = w0.y; nw[2] = w0.z; nw[3] = w0.w; nw[4] = w1.x; nw[5] = w1.y; nw[6] = w1.z; nw[7] = w1.w;
-    }
-    const float lam = A.mix == 2 ? A.lambda[0] : 0.f;
     const size_t plane = (size_t)A.G * A.block_size * A.d;
     const bf16 zero = __float2bfloat16_rn(0.f);
 #pragma unroll
