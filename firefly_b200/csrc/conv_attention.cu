@@ -177,50 +177,84 @@ __global__ void conv_norm_store_vec8_kernel(ConvHeadArgs A, bf16* __restrict__ q
     float acc[TT][8];
 #pragma unroll
     for (int i = 0; i < TT; ++i) {
-        const int t = t_begin + i, sq = row_seq[keep + i];
-        page[i] = A.block_table[(size_t)sq * A.max_blocks + pos[i] / A.block_size];
+        page[i] = A.block_table[(size_t)row_seq[keep + i] * A.max_blocks + pos[i] / A.block_size];
 #pragma unroll
         for (int e = 0; e < 8; ++e) acc[i][e] = 0.f;
-        if (active && i < n) {
+    }
+    // row by row: a row is widened once and goes into every token of the block that reads it (tap j = row - token)
+    bool outside = false;                     // some token of the block reads rows in front of its portion (the same for all threads)
 #pragma unroll
-            for (int j = 0; j < TAPS; ++j) {
-                const int tt = t - keep + j;
-                float u[8];
-                if (row_seq[i + j] == sq) {
-                    const bf16* r = reinterpret_cast<const bf16*>(&raw[i + j]);
+    for (int r = 0; r < NR; ++r) {
+        float u[8];
+        {
+            const bf16* rr = reinterpret_cast<const bf16*>(&raw[r]);
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) u[e] = __bfloat162float(r[e]);
-                } else if (A.seq_fresh[sq] == 0) {
-                    const float* row = state + (size_t)A.state_slots[sq] * A.state_stride + A.conv_off +
-                                       (size_t)(keep + (tt - A.cu_q[sq])) * C + c;
-                    *reinterpret_cast<float4*>(&u[0]) = *reinterpret_cast<const float4*>(row);
-                    *reinterpret_cast<float4*>(&u[4]) = *reinterpret_cast<const float4*>(row + 4);
-                } else {
+            for (int e = 0; e < 8; ++e) u[e] = __bfloat162float(rr[e]);
+        }
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) u[e] = 0.f;
-                }
+        for (int i = 0; i < TT; ++i) {
+            const int j = r - i;
+            if (j < 0 || j >= TAPS) continue;
+            if (row_seq[r] == row_seq[keep + i]) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc[i][e] += wr[j][e] * u[e];
+            } else if (i < n) {
+                outside = true;
             }
         }
     }
-    // every token's two sums of squares in one reduction over the block
+    if (outside && active) {
+        // the rows in front of a portion come from the sequence's slot (zeros for a fresh request)
+#pragma unroll 1
+        for (int i = 0; i < n; ++i) {
+            const int sq = row_seq[keep + i];
+            if (A.seq_fresh[sq] != 0) continue;
+            const int t0 = A.cu_q[sq];
+            const float* st = state + (size_t)A.state_slots[sq] * A.state_stride + A.conv_off;
+#pragma unroll 1
+            for (int j = 0; j < keep; ++j) {
+                const int tt = t_begin + i - keep + j;
+                if (tt >= t0) continue;
+                const float* row = st + (size_t)(keep + (tt - t0)) * C + c;
+                const float4 s0 = *reinterpret_cast<const float4*>(row), s1 = *reinterpret_cast<const float4*>(row + 4);
+                const float su[8] = {s0.x, s0.y, s0.z, s0.w, s1.x, s1.y, s1.z, s1.w};
+#pragma unroll
+                for (int ii = 0; ii < TT; ++ii) {
+                    if (ii != i) continue;
+#pragma unroll
+                    for (int jj = 0; jj < keep; ++jj) {
+                        if (jj != j) continue;
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) acc[ii][e] += wr[jj][e] * su[e];
+                    }
+                }
+            }
+        }
+    }
+    // every token's two sums of squares in one reduction over the block; a warp that holds no channel of q (of k)
+    // leaves that sum out
+    const bool warp_q = __any_sync(0xffffffffu, active && is_q), warp_k = __any_sync(0xffffffffu, active && is_k);
     float part[2 * TT];
 #pragma unroll
     for (int i = 0; i < TT; ++i) {
         float ssq = 0.f;
 #pragma unroll
         for (int e = 0; e < 8; ++e) ssq += acc[i][e] * acc[i][e];
-        part[2 * i] = warp_sum(active && is_q ? ssq : 0.f);
-        part[2 * i + 1] = warp_sum(active && is_k ? ssq : 0.f);
+        part[2 * i] = warp_q ? warp_sum(active && is_q ? ssq : 0.f) : 0.f;
+        part[2 * i + 1] = warp_k ? warp_sum(active && is_k ? ssq : 0.f) : 0.f;
     }
     if (lane == 0) {
 #pragma unroll
         for (int v = 0; v < 2 * TT; ++v) scratch[v][warp] = part[v];
     }
     __syncthreads();
+    {
+        float mine = 0.f;                      // lane v adds up sum v over the warps, in the warps' order
+        if (lane < 2 * TT)
+            for (int w = 0; w < nwarps; ++w) mine += scratch[lane][w];
 #pragma unroll
-    for (int v = 0; v < 2 * TT; ++v) part[v] = warp_sum(lane < nwarps ? scratch[v][lane] : 0.f);
+        for (int v = 0; v < 2 * TT; ++v) part[v] = __shfl_sync(0xffffffffu, mine, v);
+    }
     const size_t plane = (size_t)A.G * A.block_size * A.d;
     const bf16 zero = __float2bfloat16_rn(0.f);
 #pragma unroll
