@@ -15,7 +15,9 @@
 //
 // One block per (sequence, head, share of the value columns).  Value column j is held by PARTS neighbouring
 // threads, each with NP / PARTS key channels of column j in registers; the two sums over key channels of a
-// token (the prediction and the read-out) are joined over those threads by shuffles.
+// token (the prediction and the read-out) are joined over those threads by shuffles.  For keys of 128 and more a
+// thread holds the same key channels of two neighbouring columns: what it reads of the staged q, k and g serves
+// both, and a head needs half the blocks.
 #include "common.cuh"
 
 namespace ff {
@@ -37,19 +39,20 @@ struct DeltaArgs {
 constexpr int DR_CHUNK = 8;
 constexpr int DR_MAX_THREADS = 512;
 
-struct DeltaPlan { int NP, PARTS, vsplit, Vb, threads; };
+struct DeltaPlan { int NP, PARTS, VJ, vsplit, Vb, threads; };
 static inline bool delta_plan(int N, int V, DeltaPlan* p) {
     if (N <= 0 || N > 256 || V <= 0 || V > 256) return false;
     p->NP = N <= 16 ? 16 : (N <= 32 ? 32 : (N <= 64 ? 64 : (N <= 128 ? 128 : 256)));
     p->PARTS = p->NP >= 128 ? 16 : (p->NP >= 32 ? 8 : 4);
-    const int max_cols = DR_MAX_THREADS / p->PARTS;
+    p->VJ = p->NP >= 128 ? 2 : 1;              // value columns a thread: long keys share their staged q, k, g over two
+    const int max_cols = DR_MAX_THREADS / p->PARTS * p->VJ;
     p->vsplit = (V + max_cols - 1) / max_cols;
     p->Vb = (V + p->vsplit - 1) / p->vsplit;
-    p->threads = ((p->Vb * p->PARTS + 31) / 32) * 32;
+    p->threads = (((p->Vb + p->VJ - 1) / p->VJ * p->PARTS + 31) / 32) * 32;
     return true;
 }
 
-template <typename T, int NP, int PARTS>
+template <typename T, int NP, int PARTS, int VJ>
 __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     DeltaArgs A, float* __restrict__ state, size_t state_stride, int state_off, const int* __restrict__ cu_q,
     const int* __restrict__ state_slots, const int* __restrict__ seq_fresh, float* __restrict__ o /*[T, heads*V]*/,
@@ -63,16 +66,22 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int jl = tid / PARTS, part = tid % PARTS;
-    const int j0 = blockIdx.z * Vb, j = j0 + jl;
+    const int j0 = blockIdx.z * Vb;                       // the block's first column; the thread's are j0 + jl * VJ + x
     const int t0 = cu_q[s], t1 = cu_q[s + 1];
-    const bool live = jl < Vb && j < V;
-    const bool fresh = seq_fresh[s] != 0;
-    // a block's share of a head's state is kept as its threads hold it: register i of thread tid at i * threads + tid
-    float* S_g = state + (size_t)state_slots[s] * state_stride + state_off +
-                 ((size_t)h * gridDim.z + blockIdx.z) * KP * nthr;
-    float S[KP];
+    bool live[VJ];
 #pragma unroll
-    for (int i = 0; i < KP; ++i) S[i] = fresh ? 0.f : S_g[(size_t)i * nthr + tid];
+    for (int x = 0; x < VJ; ++x) live[x] = jl * VJ + x < Vb && j0 + jl * VJ + x < V;
+    const bool fresh = seq_fresh[s] != 0;
+    // a block's share of a head's state is kept as its threads hold it: register (x, i) of thread tid at
+    // (x * KP + i) * threads + tid
+    float* S_g = state + (size_t)state_slots[s] * state_stride + state_off +
+                 ((size_t)h * gridDim.z + blockIdx.z) * KP * VJ * nthr;
+    float S[VJ][KP];
+#pragma unroll
+    for (int x = 0; x < VJ; ++x) {
+#pragma unroll
+        for (int i = 0; i < KP; ++i) S[x][i] = fresh ? 0.f : S_g[(size_t)(x * KP + i) * nthr + tid];
+    }
     const int group = h / A.heads_per_group;
     const T* qp = pdl_fresh((const T*)A.q) + A.q_off + (size_t)group * N;
     const T* kp = pdl_fresh((const T*)A.k) + A.k_off + (size_t)group * N;
@@ -123,11 +132,18 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
         __syncthreads();
 #pragma unroll 1
         for (int c = 0; c < n; ++c) {
-            const float vj = live ? s_v[c][jl] : 0.f;
+            float vj[VJ];
+#pragma unroll
+            for (int x = 0; x < VJ; ++x) vj[x] = live[x] ? s_v[c][jl * VJ + x] : 0.f;
             const float beta = s_b[c];
             // one walk over the decayed state gives both sums over key channels: the prediction S^T k and the
             // read-out of the state before the write, S^T q; the write k u^T then adds u (k . q) to the read-out
-            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f, a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+            float d[VJ][4], a[VJ][4];
+#pragma unroll
+            for (int x = 0; x < VJ; ++x) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { d[x][e] = 0.f; a[x][e] = 0.f; }
+            }
 #pragma unroll
             for (int i = 0; i < KP; i += 4) {
                 // thread `part` holds key channels 4 PARTS m + 4 part + e (m = i / 4, e < 4)
@@ -135,33 +151,58 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
                 const float4 g4 = *reinterpret_cast<const float4*>(&s_g[c][at]);
                 const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
                 const float4 q4 = *reinterpret_cast<const float4*>(&s_q[c][at]);
-                S[i]     *= g4.x;  d0 += k4.x * S[i];      a0 += q4.x * S[i];
-                S[i + 1] *= g4.y;  d1 += k4.y * S[i + 1];  a1 += q4.y * S[i + 1];
-                S[i + 2] *= g4.z;  d2 += k4.z * S[i + 2];  a2 += q4.z * S[i + 2];
-                S[i + 3] *= g4.w;  d3 += k4.w * S[i + 3];  a3 += q4.w * S[i + 3];
+#pragma unroll
+                for (int x = 0; x < VJ; ++x) {
+                    S[x][i]     *= g4.x;  d[x][0] += k4.x * S[x][i];      a[x][0] += q4.x * S[x][i];
+                    S[x][i + 1] *= g4.y;  d[x][1] += k4.y * S[x][i + 1];  a[x][1] += q4.y * S[x][i + 1];
+                    S[x][i + 2] *= g4.z;  d[x][2] += k4.z * S[x][i + 2];  a[x][2] += q4.z * S[x][i + 2];
+                    S[x][i + 3] *= g4.w;  d[x][3] += k4.w * S[x][i + 3];  a[x][3] += q4.w * S[x][i + 3];
+                }
             }
-            float dot = (d0 + d1) + (d2 + d3), acc = (a0 + a1) + (a2 + a3);
+            float dot[VJ], acc[VJ];
+#pragma unroll
+            for (int x = 0; x < VJ; ++x) {
+                dot[x] = (d[x][0] + d[x][1]) + (d[x][2] + d[x][3]);
+                acc[x] = (a[x][0] + a[x][1]) + (a[x][2] + a[x][3]);
+            }
 #pragma unroll
             for (int off = 1; off < PARTS; off <<= 1) {
-                dot += __shfl_xor_sync(0xffffffffu, dot, off);
-                acc += __shfl_xor_sync(0xffffffffu, acc, off);
+#pragma unroll
+                for (int x = 0; x < VJ; ++x) {
+                    dot[x] += __shfl_xor_sync(0xffffffffu, dot[x], off);
+                    acc[x] += __shfl_xor_sync(0xffffffffu, acc[x], off);
+                }
             }
-            const float u = beta * (vj - dot);
-            acc += u * s_kq[c];
+            float u[VJ];
+#pragma unroll
+            for (int x = 0; x < VJ; ++x) {
+                u[x] = beta * (vj[x] - dot[x]);
+                acc[x] += u[x] * s_kq[c];
+            }
 #pragma unroll
             for (int i = 0; i < KP; i += 4) {
                 const int at = i * PARTS + part * 4;
                 const float4 k4 = *reinterpret_cast<const float4*>(&s_k[c][at]);
-                S[i]     += k4.x * u;
-                S[i + 1] += k4.y * u;
-                S[i + 2] += k4.z * u;
-                S[i + 3] += k4.w * u;
+#pragma unroll
+                for (int x = 0; x < VJ; ++x) {
+                    S[x][i]     += k4.x * u[x];
+                    S[x][i + 1] += k4.y * u[x];
+                    S[x][i + 2] += k4.z * u[x];
+                    S[x][i + 3] += k4.w * u[x];
+                }
             }
-            if (live && part == 0) o[(size_t)(c0 + c) * heads * V + (size_t)h * V + j] = acc;
+            if (part == 0) {
+#pragma unroll
+                for (int x = 0; x < VJ; ++x)
+                    if (live[x]) o[(size_t)(c0 + c) * heads * V + (size_t)h * V + j0 + jl * VJ + x] = acc[x];
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < KP; ++i) S_g[(size_t)i * nthr + tid] = S[i];
+    for (int x = 0; x < VJ; ++x) {
+#pragma unroll
+        for (int i = 0; i < KP; ++i) S_g[(size_t)(x * KP + i) * nthr + tid] = S[x][i];
+    }
 }
 
 // y[t, h*V + i] = o[t, h*V + i] / sqrt(mean_i o[t, h, :]^2 + eps) * w[i] * sigmoid(gate[t, gate_off + h*V + i]):
@@ -193,7 +234,7 @@ using namespace ff;
 FF_EXPORT long long ff_delta_state_floats(int heads, int N, int V) {
     DeltaPlan p;
     if (!delta_plan(N, V, &p)) return -1;
-    return (long long)heads * p.vsplit * (p.NP / p.PARTS) * p.threads;
+    return (long long)heads * p.vsplit * (p.NP / p.PARTS) * p.VJ * p.threads;
 }
 
 template <typename T>
@@ -204,15 +245,15 @@ static int delta_launch(const DeltaArgs& A, float* state, long long state_stride
     if (!delta_plan(N, V, &p)) return FF_ERR_UNSUPPORTED;
     if (p.Vb > 128) return FF_ERR_UNSUPPORTED;
     dim3 grid(n_seqs, heads, p.vsplit);
-#define FF_DELTA(NP, PARTS)                                                                                    \
-    FF_LAUNCH((delta_rule_scan_kernel<T, NP, PARTS>), grid, p.threads, 0, stream, A, state, (size_t)state_stride, \
+#define FF_DELTA(NP, PARTS, VJ)                                                                                    \
+    FF_LAUNCH((delta_rule_scan_kernel<T, NP, PARTS, VJ>), grid, p.threads, 0, stream, A, state, (size_t)state_stride, \
               state_off, cu_q, state_slots, seq_fresh, o, heads, N, V, p.Vb)
     switch (p.NP) {
-        case 16: FF_DELTA(16, 4); break;
-        case 32: FF_DELTA(32, 8); break;
-        case 64: FF_DELTA(64, 8); break;
-        case 128: FF_DELTA(128, 16); break;
-        case 256: FF_DELTA(256, 16); break;
+        case 16: FF_DELTA(16, 4, 1); break;
+        case 32: FF_DELTA(32, 8, 1); break;
+        case 64: FF_DELTA(64, 8, 1); break;
+        case 128: FF_DELTA(128, 16, 2); break;
+        case 256: FF_DELTA(256, 16, 2); break;
         default: return FF_ERR_UNSUPPORTED;
     }
 #undef FF_DELTA

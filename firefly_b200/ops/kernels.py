@@ -1210,16 +1210,17 @@ def delta_plan(N: int, V: int):
         raise KernelError(f"delta rule: key size {N} / value size {V} not supported (up to 256 each)")
     pad = 16 if N <= 16 else (32 if N <= 32 else (64 if N <= 64 else (128 if N <= 128 else 256)))
     parts = 16 if pad >= 128 else (8 if pad >= 32 else 4)
-    max_cols = 512 // parts
+    vj = 2 if pad >= 128 else 1                 # value columns a thread
+    max_cols = 512 // parts * vj
     vsplit = -(-V // max_cols)
     vb = -(-V // vsplit)
-    return pad, parts, vsplit, vb, -(-(vb * parts) // 32) * 32
+    return pad, parts, vsplit, vb, -(-(-(-vb // vj) * parts) // 32) * 32
 
 
 def delta_state_floats_plan(heads: int, N: int, V: int) -> int:
     """Floats of a request's state for `heads` heads of key size N and value size V (worked out on the host)."""
     pad, parts, vsplit, _, threads = delta_plan(N, V)
-    return heads * vsplit * (pad // parts) * threads
+    return heads * vsplit * (pad // parts) * (2 if pad >= 128 else 1) * threads
 
 
 def delta_state_floats(heads: int, N: int, V: int) -> int:
