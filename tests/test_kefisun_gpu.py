@@ -67,6 +67,13 @@ CONFIGS = {
     # attention only: every layer blends with the first layer's values
     "attention_only": _cfg([_with(_att(4, 4, 16, 16, 64), _dense(48)), _with(_att(8, 4, 16, 16, 33, conv=2), None),
                             _with(_att(4, 4, 32, 16, 16), _dense(48))], taps=4),
+    # sizes that every fast path takes in bfloat16: heads of 64 (the tcgen05 attention kernel with the bias, the
+    # 16-byte forms of the head preparation, the gate and the activation), blending layers with value heads as long as
+    # and shorter than key heads, a recurrent layer with a key of 128 (two value columns a thread)
+    "fast_paths": _cfg([_with(_att(4, 2, 64, 64, 70, conv=4), _dense(72)),
+                        _with(_delta(2, 1, 128, 64, conv=4), None),
+                        _with(_att(8, 2, 64, 64, 33, conv=3), _dense(64)),
+                        _with(_att(2, 2, 128, 64, 100, conv=2), None)], width=64, vocab=97, taps=4),
 }
 RANKS = {"both_mixers": {"a": 8, "g": 12}, "odd_sizes": {"a": 5, "g": 3}}
 
