@@ -37,6 +37,7 @@ struct DeltaArgs {
 };
 
 constexpr int DR_CHUNK = 8;
+constexpr int DR_AHEAD = 2;     // elements of a chunk's inputs a thread may hold for the chunk to come
 constexpr int DR_MAX_THREADS = 512;
 
 struct DeltaPlan { int NP, PARTS, VJ, vsplit, Vb, threads; };
@@ -91,10 +92,45 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     const float* dtb = A.dt_bias + (size_t)h * N;
     const int cols = min(Vb, V - j0);
     const float rate = expf(A.a_log[h]);
+    // Where a chunk's inputs are at most DR_AHEAD elements a thread, the next chunk's are asked for (into registers)
+    // before the current chunk's tokens are walked, so that their way from memory passes under the recurrence.
+    const bool ahead = DR_CHUNK * NP <= DR_AHEAD * nthr && DR_CHUNK * cols <= DR_AHEAD * nthr;
+    T nq[DR_AHEAD], nk[DR_AHEAD], nv[DR_AHEAD], nb = from_float<T>(0.f);
+    float na[DR_AHEAD];
+    auto ask = [&](int c0) {
+        const int n = min(DR_CHUNK, t1 - c0);
+#pragma unroll
+        for (int r = 0; r < DR_AHEAD; ++r) {
+            const int idx = tid + r * nthr, c = idx / NP, i = idx - c * NP;
+            const bool in = idx < DR_CHUNK * NP && c < n && i < N;
+            nq[r] = in ? qp[(size_t)(c0 + c) * A.q_stride + i] : from_float<T>(0.f);
+            nk[r] = in ? kp[(size_t)(c0 + c) * A.k_stride + i] : from_float<T>(0.f);
+            na[r] = in ? ap[(size_t)(c0 + c) * A.a_stride + i] : 0.f;
+            const int cv = idx / cols, jj = idx - cv * cols;
+            nv[r] = (idx < DR_CHUNK * cols && cv < n) ? vp[(size_t)(c0 + cv) * A.v_stride + jj] : from_float<T>(0.f);
+        }
+        nb = tid < n ? bp[(size_t)(c0 + tid) * A.beta_stride] : from_float<T>(0.f);
+    };
+    if (ahead && t0 < t1) ask(t0);
     for (int c0 = t0; c0 < t1; c0 += DR_CHUNK) {
         const int n = min(DR_CHUNK, t1 - c0);
         __syncthreads();
         // staging: the chunk's q, k (raw), decays, v and beta in 32-bit
+        if (ahead) {
+#pragma unroll
+            for (int r = 0; r < DR_AHEAD; ++r) {
+                const int idx = tid + r * nthr, c = idx / NP, i = idx - c * NP;
+                if (idx < DR_CHUNK * NP) {
+                    const bool in = c < n && i < N;
+                    s_q[c][i] = to_float(nq[r]);
+                    s_k[c][i] = to_float(nk[r]);
+                    s_g[c][i] = in ? expf(-rate * dr_softplus(na[r] + dtb[i])) : 0.f;
+                }
+                if (idx < DR_CHUNK * cols) s_v[idx / cols][idx % cols] = to_float(nv[r]);
+            }
+            if (tid < DR_CHUNK) s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(nb))) : 0.f;
+            if (c0 + DR_CHUNK < t1) ask(c0 + DR_CHUNK);
+        } else {
         for (int idx = tid; idx < DR_CHUNK * NP; idx += nthr) {
             const int c = idx / NP, i = idx - c * NP;
             float qv = 0.f, kv = 0.f, gv = 0.f;
@@ -113,6 +149,7 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
         }
         if (tid < DR_CHUNK)
             s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(bp[(size_t)(c0 + tid) * A.beta_stride]))) : 0.f;
+        }
         __syncthreads();
         // unit vectors: a warp per token
         for (int c = warp; c < n; c += nwarps) {
