@@ -60,10 +60,12 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     int heads, int N, int V, int Vb) {
     pdl_prologue();
     constexpr int KP = NP / PARTS;
+    constexpr int CH = NP >= 256 ? DR_CHUNK : 2 * DR_CHUNK;     // tokens staged at a time (shared memory bounds the longest keys)
+    constexpr int AH = NP >= 256 ? DR_AHEAD : 2 * DR_AHEAD;
     static_assert(KP % 4 == 0, "a thread reads its key channels four at a time");
-    __shared__ __align__(16) float s_q[DR_CHUNK][NP], s_k[DR_CHUNK][NP], s_g[DR_CHUNK][NP];
-    __shared__ float s_v[DR_CHUNK][128];
-    __shared__ float s_b[DR_CHUNK], s_kq[DR_CHUNK];
+    __shared__ __align__(16) float s_q[CH][NP], s_k[CH][NP], s_g[CH][NP];
+    __shared__ float s_v[CH][128];
+    __shared__ float s_b[CH], s_kq[CH];
     const int s = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, nthr = blockDim.x;
     const int lane = tid & 31, warp = tid >> 5, nwarps = nthr >> 5;
     const int jl = tid / PARTS, part = tid % PARTS;
@@ -92,46 +94,46 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     const float* dtb = A.dt_bias + (size_t)h * N;
     const int cols = min(Vb, V - j0);
     const float rate = expf(A.a_log[h]);
-    // Where a chunk's inputs are at most DR_AHEAD elements a thread, the next chunk's are asked for (into registers)
+    // Where a chunk's inputs are at most AH elements a thread, the next chunk's are asked for (into registers)
     // before the current chunk's tokens are walked, so that their way from memory passes under the recurrence.
-    const bool ahead = DR_CHUNK * NP <= DR_AHEAD * nthr && DR_CHUNK * cols <= DR_AHEAD * nthr;
-    T nq[DR_AHEAD], nk[DR_AHEAD], nv[DR_AHEAD], nb = from_float<T>(0.f);
-    float na[DR_AHEAD];
+    const bool ahead = CH * NP <= AH * nthr && CH * cols <= AH * nthr;
+    T nq[AH], nk[AH], nv[AH], nb = from_float<T>(0.f);
+    float na[AH];
     auto ask = [&](int c0) {
-        const int n = min(DR_CHUNK, t1 - c0);
+        const int n = min(CH, t1 - c0);
 #pragma unroll
-        for (int r = 0; r < DR_AHEAD; ++r) {
+        for (int r = 0; r < AH; ++r) {
             const int idx = tid + r * nthr, c = idx / NP, i = idx - c * NP;
-            const bool in = idx < DR_CHUNK * NP && c < n && i < N;
+            const bool in = idx < CH * NP && c < n && i < N;
             nq[r] = in ? qp[(size_t)(c0 + c) * A.q_stride + i] : from_float<T>(0.f);
             nk[r] = in ? kp[(size_t)(c0 + c) * A.k_stride + i] : from_float<T>(0.f);
             na[r] = in ? ap[(size_t)(c0 + c) * A.a_stride + i] : 0.f;
             const int cv = idx / cols, jj = idx - cv * cols;
-            nv[r] = (idx < DR_CHUNK * cols && cv < n) ? vp[(size_t)(c0 + cv) * A.v_stride + jj] : from_float<T>(0.f);
+            nv[r] = (idx < CH * cols && cv < n) ? vp[(size_t)(c0 + cv) * A.v_stride + jj] : from_float<T>(0.f);
         }
         nb = tid < n ? bp[(size_t)(c0 + tid) * A.beta_stride] : from_float<T>(0.f);
     };
     if (ahead && t0 < t1) ask(t0);
-    for (int c0 = t0; c0 < t1; c0 += DR_CHUNK) {
-        const int n = min(DR_CHUNK, t1 - c0);
+    for (int c0 = t0; c0 < t1; c0 += CH) {
+        const int n = min(CH, t1 - c0);
         __syncthreads();
         // staging: the chunk's q, k (raw), decays, v and beta in 32-bit
         if (ahead) {
 #pragma unroll
-            for (int r = 0; r < DR_AHEAD; ++r) {
+            for (int r = 0; r < AH; ++r) {
                 const int idx = tid + r * nthr, c = idx / NP, i = idx - c * NP;
-                if (idx < DR_CHUNK * NP) {
+                if (idx < CH * NP) {
                     const bool in = c < n && i < N;
                     s_q[c][i] = to_float(nq[r]);
                     s_k[c][i] = to_float(nk[r]);
                     s_g[c][i] = in ? expf(-rate * dr_softplus(na[r] + dtb[i])) : 0.f;
                 }
-                if (idx < DR_CHUNK * cols) s_v[idx / cols][idx % cols] = to_float(nv[r]);
+                if (idx < CH * cols) s_v[idx / cols][idx % cols] = to_float(nv[r]);
             }
-            if (tid < DR_CHUNK) s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(nb))) : 0.f;
-            if (c0 + DR_CHUNK < t1) ask(c0 + DR_CHUNK);
+            if (tid < CH) s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(nb))) : 0.f;
+            if (c0 + CH < t1) ask(c0 + CH);
         } else {
-        for (int idx = tid; idx < DR_CHUNK * NP; idx += nthr) {
+        for (int idx = tid; idx < CH * NP; idx += nthr) {
             const int c = idx / NP, i = idx - c * NP;
             float qv = 0.f, kv = 0.f, gv = 0.f;
             if (c < n && i < N) {
@@ -143,11 +145,11 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
             s_k[c][i] = kv;
             s_g[c][i] = gv;
         }
-        for (int idx = tid; idx < DR_CHUNK * cols; idx += nthr) {
+        for (int idx = tid; idx < CH * cols; idx += nthr) {
             const int c = idx / cols, jj = idx - c * cols;
             s_v[c][jj] = c < n ? to_float(vp[(size_t)(c0 + c) * A.v_stride + jj]) : 0.f;
         }
-        if (tid < DR_CHUNK)
+        if (tid < CH)
             s_b[tid] = tid < n ? 1.0f / (1.0f + expf(-to_float(bp[(size_t)(c0 + tid) * A.beta_stride]))) : 0.f;
         }
         __syncthreads();
