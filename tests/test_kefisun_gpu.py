@@ -354,7 +354,7 @@ def _window_case(tmp_path, dtype, window, far, query, sizes):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("shape", [(4, 2, 24, 16, 4), (2, 2, 16, 40, 2), (5, 1, 40, 12, 3), (8, 2, 64, 64, 4), (1, 1, 128, 128, 1),
-                                   (34, 2, 16, 16, 2)])
+                                   (34, 2, 16, 16, 2), (3, 1, 80, 72, 4), (2, 1, 192, 64, 3), (2, 2, 100, 256, 2)])
 def test_attention_alone_in_other_sizes_whole_in_portions_and_token_by_token(tmp_path, dtype, shape):
     heads, kv, dim, vdim, conv = shape
     layer = _with(_att(heads, kv, dim, vdim, 23, conv=conv, v_mix=False), None)
