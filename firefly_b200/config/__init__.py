@@ -2,8 +2,9 @@ from .base import (ConfigError, LayerSpec, ModelConfig, ModelSpec, PartSpec, Sch
                    read_config_json)
 from .kefisun import KefisunConfig
 from .kolorax import KoloraxConfig
+from .papusun import PapusunConfig
 from .pepolorn import PepolornConfig
 from .qwen3 import Qwen3Config
 
 __all__ = ["ConfigError", "LayerSpec", "ModelConfig", "ModelSpec", "PartSpec", "ScheduleEntry",
-           "KefisunConfig", "KoloraxConfig", "PepolornConfig", "Qwen3Config", "read_config_json"]
+           "KefisunConfig", "KoloraxConfig", "PapusunConfig", "PepolornConfig", "Qwen3Config", "read_config_json"]

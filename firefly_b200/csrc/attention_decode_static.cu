@@ -76,7 +76,7 @@ int ff_attn_decode_static(const void* q, int q_stride, const void* cache, const 
     attn_decode_kernel<<<grid, NTHREADS, DECODE_SMEM, stream>>>(
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
         out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits,
-        (const float*)nullptr, 0, (int*)nullptr);
+        (const float*)nullptr, 0, 0.0f, (int*)nullptr);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);

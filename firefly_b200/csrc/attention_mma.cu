@@ -124,7 +124,10 @@ struct WarpState {
         for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
         m[0] = m[1] = -CUDART_INF_F;
         l[0] = l[1] = 0.f;
+        cap = 0.f;
     }
+    // a cap on the scores (in the units of the scaled scores, log2 e included; 0: none): v <- cap * tanh(v / cap)
+    float cap;
 
     // Qs: this warp's 16 rows of q in smem ([16][KSTR]); Ks/Vs: this warp's KN keys.
     // key0: absolute index of the warp's first key.  Row r of the fragment (g, g+8)
@@ -162,6 +165,7 @@ struct WarpState {
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 float v = s[j][e] * scale_log2;
+                if (cap != 0.f) v = capped_score(v, cap);
                 const int key = key0 + j * 8 + 2 * t4 + (e & 1);
                 bool visible = true;
                 if (need_mask) {
@@ -236,7 +240,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
                   const int* __restrict__ block_table, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride,
                   int nq, int nkv, int block_size, int num_blocks, float scale_log2, int window,
-                  const float* __restrict__ dist_bias, int bias_len, int* __restrict__ status) {
+                  const float* __restrict__ dist_bias, int bias_len, float softcap_log2, int* __restrict__ status) {
     pdl_prologue();
     extern __shared__ __align__(16) unsigned char smem_raw[];
     bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][KSTR]
@@ -325,6 +329,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
 
     WarpState<BN> st;
     st.init();
+    st.cap = softcap_log2;
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
@@ -388,6 +393,7 @@ struct DecodeHeads {
     int* status;               // 2: page of the newest token missing, 3: position beyond the table, 4: a key's page missing
     const float* dist_bias;    // [nq][bias_len] or null: a bias by distance taken off the scores (see WarpState::step)
     int bias_len;
+    float softcap_log2;        // a cap on the scaled scores (log2 e included), 0: none
 };
 constexpr int HC = D / 64;     // elements of each half of a head that a lane holds (heads finished in a warp)
 
@@ -661,6 +667,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     }
     WarpState<16> st;
     st.init();
+    st.cap = hd.softcap_log2;
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
@@ -753,11 +760,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
                    const int* __restrict__ ctx_lens, bf16* __restrict__ out, int out_stride,
                    float* __restrict__ part_o, float* __restrict__ part_ml, int nq, int nkv,
                    int block_size, int num_blocks, float scale_log2, int window, int num_splits,
-                   const float* __restrict__ dist_bias, int bias_len, int* __restrict__ status) {
+                   const float* __restrict__ dist_bias, int bias_len, float softcap_log2, int* __restrict__ status) {
     DecodeHeads hd{};
     hd.status = status;           // may be null: a missing page is then not reported
     hd.dist_bias = dist_bias;
     hd.bias_len = bias_len;
+    hd.softcap_log2 = softcap_log2;
     attn_decode_body<false, false>(q, q_stride, cache, block_table, max_blocks, cu_q, ctx_lens, out, out_stride,
                                    part_o, part_ml, nq, nkv, block_size, num_blocks, scale_log2, window, num_splits,
                                    hd, DecodeUnits{});
@@ -960,14 +968,14 @@ FF_EXPORT int ff_attn_tiled(const void* q, int q_stride, const void* cache, cons
                             int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs,
                             int total_tiles, void* out, int out_stride, int nq, int nkv, int block_size,
                             int num_blocks, float scale, int window, const float* dist_bias, int bias_len,
-                            int* status, cudaStream_t stream) {
+                            float softcap, int* status, cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     FF_SMEM_LIMIT(attn_tiled_kernel, TILED_SMEM);
     dim3 grid(total_tiles, nkv);
     FF_LAUNCH((attn_tiled_kernel), grid, NTHREADS, TILED_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, n_seqs,
-        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window, dist_bias, bias_len, status);
+        (bf16*)out, out_stride, nq, nkv, block_size, num_blocks, scale * LOG2E, window, dist_bias, bias_len, softcap * LOG2E, status);
     FF_LAUNCH_CHECK();
     return 0;
 }
@@ -978,7 +986,7 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
                              int max_blocks, const int* cu_q, const int* ctx_lens, int n_seqs, void* out,
                              int out_stride, float* part_o, float* part_ml, int nq, int nkv,
                              int block_size, int num_blocks, float scale, int window, int num_splits,
-                             const float* dist_bias, int bias_len, int* status, cudaStream_t stream) {
+                             const float* dist_bias, int bias_len, float softcap, int* status, cudaStream_t stream) {
     if (n_seqs <= 0) return 0;
     if (nkv <= 0 || nq % nkv || num_splits < 1 || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     if (nq / nkv > 16) return FF_ERR_UNSUPPORTED;
@@ -987,7 +995,7 @@ FF_EXPORT int ff_attn_decode(const void* q, int q_stride, const void* cache, con
     FF_LAUNCH((attn_decode_kernel), grid, NTHREADS, DECODE_SMEM, stream, 
         (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, cu_q, ctx_lens, (bf16*)out,
         out_stride, part_o, part_ml, nq, nkv, block_size, num_blocks, scale * LOG2E, window, num_splits, dist_bias,
-        bias_len, status);
+        bias_len, softcap * LOG2E, status);
     FF_LAUNCH_CHECK();
     if (num_splits > 1) {
         dim3 cgrid(n_seqs, nq);
@@ -1047,7 +1055,7 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
                                    int nkv, int block_size, int num_blocks, float scale, int window, int units,
                                    int max_ranges, int finish_heads, const float* q_norm_w,
                                    const float* k_norm_w, float eps, const float* cos_sin, int max_positions,
-                                   const float* dist_bias, int bias_len, int* status, cudaStream_t stream) {
+                                   const float* dist_bias, int bias_len, float softcap, int* status, cudaStream_t stream) {
     if (FF_KV_PLANES != 2 && finish_heads) return FF_ERR_UNSUPPORTED;
     if (n_seqs <= 0) return 0;
     if (dist_bias && (window <= 0 || bias_len < window)) return FF_ERR_BAD_ARG;
@@ -1060,7 +1068,7 @@ FF_EXPORT int ff_attn_decode_units(const void* q, int q_stride, void* cache, con
     if (finish_heads && (D % 64 != 0 || status == nullptr)) return FF_ERR_UNSUPPORTED;
     FF_SMEM_LIMIT(attn_decode_units_kernel<true>, DECODE_SMEM);
     FF_SMEM_LIMIT(attn_decode_units_kernel<false>, DECODE_SMEM);
-    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status, dist_bias, bias_len};
+    DecodeHeads hd{q_norm_w, k_norm_w, eps, cos_sin, max_positions, (bf16*)cache, status, dist_bias, bias_len, softcap * LOG2E};
     DecodeUnits un{n_seqs, max_ranges, seq_ranges, units};
     dim3 grid(nkv, units);
     if (finish_heads)

@@ -38,7 +38,7 @@ __global__ void paged_attention_simt_kernel(
     const int* __restrict__ block_table, int max_blocks, const int* __restrict__ token_seq,
     const int* __restrict__ positions, T* __restrict__ out, int out_stride, int nq, int nkv, int d,
     int block_size, int num_blocks, float scale, int window, const float* __restrict__ dist_bias, int bias_len,
-    int* __restrict__ status) {
+    float softcap, int* __restrict__ status) {
     pdl_prologue();
     q = pdl_fresh(q);              // the kernel in front writes the finished heads and this step's cache rows
     cache = pdl_fresh(cache);
@@ -78,6 +78,7 @@ __global__ void paged_attention_simt_kernel(
             if (i < d) part += qr[jj] * to_float(krow[i]);
         }
         float s = warp_sum(part) * scale;
+        if (softcap != 0.f) s = softcap * tanhf(s / softcap);      // a cap on the scaled score
         if (bias_row) s -= bias_row[pos - j];
         const float m_new = fmaxf(m, s);
         const float corr = expf(m - m_new);
@@ -123,7 +124,7 @@ FF_EXPORT int ff_paged_attention_simt(const void* q, int dtype, int q_stride, co
                                       const int* block_table, int max_blocks, const int* token_seq,
                                       const int* positions, void* out, int out_stride, int T, int nq,
                                       int nkv, int d, int block_size, int num_blocks, float scale,
-                                      int window, const float* dist_bias, int bias_len, int* status,
+                                      int window, const float* dist_bias, int bias_len, float softcap, int* status,
                                       cudaStream_t stream) {
     if (T <= 0) return 0;
     if (d <= 0 || d > ATT_MAX_D) return FF_ERR_UNSUPPORTED;
@@ -132,11 +133,11 @@ FF_EXPORT int ff_paged_attention_simt(const void* q, int dtype, int q_stride, co
     if (dtype == 0)
         FF_LAUNCH((paged_attention_simt_kernel<float>), grid, ATT_WARPS * 32, 0, stream, 
             (const float*)q, q_stride, (const float*)cache, block_table, max_blocks, token_seq,
-            positions, (float*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, status);
+            positions, (float*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, softcap, status);
     else if (dtype == 1)
         FF_LAUNCH((paged_attention_simt_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, 
             (const bf16*)q, q_stride, (const bf16*)cache, block_table, max_blocks, token_seq,
-            positions, (bf16*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, status);
+            positions, (bf16*)out, out_stride, nq, nkv, d, block_size, num_blocks, scale, window, dist_bias, bias_len, softcap, status);
     else
         return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();

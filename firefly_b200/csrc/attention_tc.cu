@@ -216,7 +216,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                const int* __restrict__ ctx_lens, int n_seqs, bf16* __restrict__ out, int out_stride, int nq,
                int nkv, int block_size, int num_blocks, float scale_log2, int window, int* __restrict__ status,
                int num_splits, float* __restrict__ part_o, float* __restrict__ part_ml,
-               const float* __restrict__ dist_bias, int bias_len) {
+               const float* __restrict__ dist_bias, int bias_len, float softcap_log2) {
     // dist_bias (float [nq][bias_len >= window], or null): entry (head, i - j) is taken off the scaled score of
     // query position i and key position j; a window lets only distances below `window` through.
     // num_splits > 1: the grid holds every (row tile, kv head) num_splits times; each copy walks its share
@@ -370,7 +370,9 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         const uint32_t lane_base = (uint32_t)((warp * 32) << 16);
         // with a bias the scores are scaled and biased as they leave tensor memory; what follows sees scale 1
         const float* brow = dist_bias ? dist_bias + (size_t)head * bias_len + pos : nullptr;   // brow[-key]
-        const float sl2 = dist_bias ? 1.0f : scale_log2;
+        // the same holds for a cap on the scores (softcap_log2, in the scaled scores' units; 0: none)
+        const bool early = dist_bias != nullptr || softcap_log2 != 0.f;
+        const float sl2 = early ? 1.0f : scale_log2;
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -387,11 +389,15 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
             tm_ld_wait();
             // mask (only tiles that touch the diagonal or a window's edge), then the row max of the raw
             // scores with four independent chains; the scale (> 0) is applied later
-            if (brow) {
+            if (early) {
 #pragma unroll
                 for (int i = 0; i < BN; ++i) {
                     const int key = key0 + i;
-                    s[i] = (key < lo || key >= hi) ? -CUDART_INF_F : fmaf(s[i], scale_log2, -__ldg(brow - key) * LOG2E);
+                    float v = s[i] * scale_log2;
+                    if (softcap_log2 != 0.f) v = capped_score(v, softcap_log2);
+                    if (key < lo || key >= hi) v = -CUDART_INF_F;
+                    else if (brow) v -= __ldg(brow - key) * LOG2E;
+                    s[i] = v;
                 }
             } else if (need_mask) {
 #pragma unroll
@@ -701,7 +707,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
                          const int* cu_q, const int* ctx_lens, int n_seqs, int total_tiles, void* out,
                          int out_stride, int nq, int nkv, int block_size, int num_blocks, float scale, int window,
                          int* status, int num_splits, float* part_o, float* part_ml, int tok_base, int n_tokens,
-                         const float* dist_bias, int bias_len, cudaStream_t stream) {
+                         const float* dist_bias, int bias_len, float softcap, cudaStream_t stream) {
     if (n_seqs <= 0 || total_tiles <= 0) return 0;
     if (nkv <= 0 || nq % nkv || (dist_bias && (window <= 0 || bias_len < window))) return FF_ERR_BAD_ARG;
     if (num_splits < 1 || (num_splits > 1 && (!part_o || !part_ml || n_tokens <= 0 || tok_base < 0))) return FF_ERR_BAD_ARG;
@@ -720,7 +726,7 @@ FF_EXPORT int ff_attn_tc(const void* q, int q_stride, const void* cache, const i
     if ((long long)total_tiles * nkv * num_splits >= (1ll << 31)) return FF_ERR_UNSUPPORTED;
     FF_LAUNCH((attn_tc_kernel), dim3((unsigned)(total_tiles * nkv * num_splits)), ATC_THREADS, ATC_SMEM, stream, arg,
               (const bf16*)q, q_stride, block_table, max_blocks, cu_q, ctx_lens, n_seqs, (bf16*)out, out_stride, nq, nkv,
-              block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml, dist_bias, bias_len);
+              block_size, num_blocks, scale * LOG2E, window, status, num_splits, part_o, part_ml, dist_bias, bias_len, softcap * LOG2E);
     if (num_splits > 1) {
         const int n_pairs = n_tokens * nq, per_block = JOIN_THREADS / (D / 4);
         FF_LAUNCH((attn_tc_join_kernel), dim3((unsigned)((n_pairs + per_block - 1) / per_block)), JOIN_THREADS, 0, stream,

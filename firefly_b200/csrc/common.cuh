@@ -131,6 +131,13 @@ __host__ __device__ __forceinline__ int first_visible_key(int pos, int window) {
     return 0;
 }
 
+// A cap on an attention score: cap * tanh(v / cap), with tanh(x) = 1 - 2 / (exp(2x) + 1) on the fast
+// exponential (absolute error of a few 1e-7 in tanh).  The 32-bit attention kernel calls tanhf instead.
+__device__ __forceinline__ float capped_score(float v, float cap) {
+    const float e = __expf(2.0f * v / cap);
+    return cap * (1.0f - __fdividef(2.0f, e + 1.0f));
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(bf16 x) { return __bfloat162float(x); }
 

@@ -1,5 +1,6 @@
 // A recurrent mixer that corrects its state by the error of its own prediction (the gated delta rule), with a
-// decay per head and key channel:
+// decay per head and key channel (or one per head: `decay_per_head`, the raw decay inputs are then rows of
+// [heads] and dt_bias has one entry a head; g_t[i] is the same for every key channel i):
 //
 //   S_t   = diag(g_t) S_(t-1)                         S: [key channel, value channel] per head, 32-bit, starts at 0
 //   u_t   = beta_t (v_t - S_t^T k_t)
@@ -34,6 +35,7 @@ struct DeltaArgs {
     const float* a_log;                          // [heads]
     int heads_per_group;
     float q_scale, unit_eps;
+    int decay_per_head;                          // 1: `a` rows of [heads], dt_bias [heads]
 };
 
 constexpr int DR_CHUNK = 8;
@@ -90,8 +92,9 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     const T* kp = pdl_fresh((const T*)A.k) + A.k_off + (size_t)group * N;
     const T* vp = pdl_fresh((const T*)A.v) + A.v_off + (size_t)h * V + j0;
     const T* bp = pdl_fresh((const T*)A.beta) + A.beta_off + h;
-    const float* ap = pdl_fresh(A.a) + A.a_off + (size_t)h * N;
-    const float* dtb = A.dt_bias + (size_t)h * N;
+    const int an = A.decay_per_head ? 0 : 1;            // 0: every key channel reads the head's one decay input
+    const float* ap = pdl_fresh(A.a) + A.a_off + (A.decay_per_head ? (size_t)h : (size_t)h * N);
+    const float* dtb = A.dt_bias + (A.decay_per_head ? (size_t)h : (size_t)h * N);
     const int cols = min(Vb, V - j0);
     const float rate = expf(A.a_log[h]);
     // Where a chunk's inputs are at most AH elements a thread, the next chunk's are asked for (into registers)
@@ -107,7 +110,7 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
             const bool in = idx < CH * NP && c < n && i < N;
             nq[r] = in ? qp[(size_t)(c0 + c) * A.q_stride + i] : from_float<T>(0.f);
             nk[r] = in ? kp[(size_t)(c0 + c) * A.k_stride + i] : from_float<T>(0.f);
-            na[r] = in ? ap[(size_t)(c0 + c) * A.a_stride + i] : 0.f;
+            na[r] = in ? ap[(size_t)(c0 + c) * A.a_stride + i * an] : 0.f;
             const int cv = idx / cols, jj = idx - cv * cols;
             nv[r] = (idx < CH * cols && cv < n) ? vp[(size_t)(c0 + cv) * A.v_stride + jj] : from_float<T>(0.f);
         }
@@ -126,7 +129,7 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
                     const bool in = c < n && i < N;
                     s_q[c][i] = to_float(nq[r]);
                     s_k[c][i] = to_float(nk[r]);
-                    s_g[c][i] = in ? expf(-rate * dr_softplus(na[r] + dtb[i])) : 0.f;
+                    s_g[c][i] = in ? expf(-rate * dr_softplus(na[r] + dtb[i * an])) : 0.f;
                 }
                 if (idx < CH * cols) s_v[idx / cols][idx % cols] = to_float(nv[r]);
             }
@@ -139,7 +142,7 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
             if (c < n && i < N) {
                 qv = to_float(qp[(size_t)(c0 + c) * A.q_stride + i]);
                 kv = to_float(kp[(size_t)(c0 + c) * A.k_stride + i]);
-                gv = expf(-rate * dr_softplus(ap[(size_t)(c0 + c) * A.a_stride + i] + dtb[i]));
+                gv = expf(-rate * dr_softplus(ap[(size_t)(c0 + c) * A.a_stride + i * an] + dtb[i * an]));
             }
             s_q[c][i] = qv;
             s_k[c][i] = kv;
@@ -244,11 +247,13 @@ __global__ void __launch_bounds__(DR_MAX_THREADS) delta_rule_scan_kernel(
     }
 }
 
-// y[t, h*V + i] = o[t, h*V + i] / sqrt(mean_i o[t, h, :]^2 + eps) * w[i] * sigmoid(gate[t, gate_off + h*V + i]):
-// a norm over each head's values with one weight row for all heads, then a sigmoid gate.  One warp per (token, head).
+// y[t, h*V + i] = o[t, h*V + i] / sqrt(mean_i o[t, h, :]^2 + eps) * w[i] * act(gate[t, gate_off + h*V + i]):
+// a norm over each head's values with one weight row for all heads, then a gate, act = sigmoid (gate_act 0) or
+// SiLU (gate_act 1).  One warp per (token, head).
 template <typename T>
 __global__ void head_norm_gate_kernel(const float* o, const float* gate, int gate_stride, int gate_off,
-                                      const float* __restrict__ w, float eps, T* __restrict__ y, int rows, int heads, int V) {
+                                      const float* __restrict__ w, float eps, T* __restrict__ y, int rows, int heads, int V,
+                                      int gate_act) {
     pdl_prologue();
     o = pdl_fresh(o);
     gate = pdl_fresh(gate);
@@ -261,8 +266,10 @@ __global__ void head_norm_gate_kernel(const float* o, const float* gate, int gat
     for (int i = lane; i < V; i += 32) ss += orow[i] * orow[i];
     ss = warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)V + eps);
-    for (int i = lane; i < V; i += 32)
-        y[(size_t)row * V + i] = from_float<T>(orow[i] * inv * w[i] / (1.0f + expf(-grow[i])));
+    for (int i = lane; i < V; i += 32) {
+        const float g = grow[i], sg = 1.0f / (1.0f + expf(-g));
+        y[(size_t)row * V + i] = from_float<T>(orow[i] * inv * w[i] * (gate_act ? g * sg : sg));
+    }
 }
 
 }  // namespace ff
@@ -303,14 +310,14 @@ static int delta_launch(const DeltaArgs& A, float* state, long long state_stride
 FF_EXPORT int ff_delta_rule_scan(const void* q, int q_stride, int q_off, const void* k, int k_stride, int k_off,
                                  const void* v, int v_stride, int v_off, const void* beta, int beta_stride, int beta_off,
                                  int dtype, const float* a, int a_stride, int a_off, const float* dt_bias,
-                                 const float* a_log, int heads_per_group, float q_scale, float unit_eps, float* state,
+                                 const float* a_log, int decay_per_head, int heads_per_group, float q_scale, float unit_eps, float* state,
                                  long long state_stride, int state_off, const int* cu_q, const int* state_slots,
                                  const int* seq_fresh, float* o, int T, int n_seqs, int heads, int N, int V,
                                  cudaStream_t stream) {
     if (T <= 0 || n_seqs <= 0) return 0;
     if (heads_per_group <= 0 || heads % heads_per_group) return FF_ERR_BAD_ARG;
     DeltaArgs A{q, q_stride, q_off, k, k_stride, k_off, v, v_stride, v_off, beta, beta_stride, beta_off,
-                a, a_stride, a_off, dt_bias, a_log, heads_per_group, q_scale, unit_eps};
+                a, a_stride, a_off, dt_bias, a_log, heads_per_group, q_scale, unit_eps, decay_per_head ? 1 : 0};
     if (dtype == 0)
         return delta_launch<float>(A, state, state_stride, state_off, cu_q, state_slots, seq_fresh, o, n_seqs, heads, N, V, stream);
     if (dtype == 1)
@@ -319,15 +326,15 @@ FF_EXPORT int ff_delta_rule_scan(const void* q, int q_stride, int q_off, const v
 }
 
 FF_EXPORT int ff_head_norm_gate(const float* o, const float* gate, int gate_stride, int gate_off, const float* w, float eps,
-                                void* y, int dtype, int T, int heads, int V, cudaStream_t stream) {
+                                void* y, int dtype, int T, int heads, int V, int gate_act, cudaStream_t stream) {
     const int rows = T * heads;
     if (rows <= 0) return 0;
     const int warps = 4;
     const unsigned blocks = (unsigned)((rows + warps - 1) / warps);
     if (dtype == 0)
-        FF_LAUNCH((head_norm_gate_kernel<float>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (float*)y, rows, heads, V);
+        FF_LAUNCH((head_norm_gate_kernel<float>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (float*)y, rows, heads, V, gate_act);
     else if (dtype == 1)
-        FF_LAUNCH((head_norm_gate_kernel<bf16>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (bf16*)y, rows, heads, V);
+        FF_LAUNCH((head_norm_gate_kernel<bf16>), blocks, warps * 32, 0, stream, o, gate, gate_stride, gate_off, w, eps, (bf16*)y, rows, heads, V, gate_act);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;

@@ -407,6 +407,30 @@ __global__ void glu_act_kernel(const T* gu, const float* __restrict__ bias, T* _
     out[idx] = from_float<T>(a * u);
 }
 
+// out[t, j] = act(g[t, j]) * table[ids[t], col0 + j] for j < n: a projection's rows gated into the rows that a table
+// holds per token id (one slice of `n` columns of a wider table).  act 0: SiLU, 1: the tanh form of GELU; 32-bit
+// arithmetic.  An id outside the table raises status 1 and reads row 0.
+template <typename T>
+__global__ void act_mul_table_rows_kernel(const T* g, const int* __restrict__ ids, const T* __restrict__ table,
+                                          int table_cols, int col0, int vocab, T* __restrict__ out, int n, size_t total,
+                                          int act, int* __restrict__ status) {
+    pdl_prologue();
+    g = pdl_fresh(g);
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const size_t t = idx / n;
+    const int j = (int)(idx - t * n);
+    int id = ids[t];
+    if (id < 0 || id >= vocab) {
+        if (j == 0) atomicExch(status, 1);
+        id = 0;
+    }
+    const float z = to_float(g[idx]);
+    const float a = act == 0 ? z / (1.0f + expf(-z))
+                             : 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    out[idx] = from_float<T>(a * to_float(table[(size_t)id * table_cols + col0 + j]));
+}
+
 // Eight bfloat16 outputs a thread (I % 8 == 0, rows 16-byte aligned): 16-byte loads and stores, the form long
 // prompts use.  The arithmetic is that of glu_act_kernel, element by element.
 template <int ACT>
@@ -515,6 +539,23 @@ FF_EXPORT int ff_glu_act(const void* gate_up, const float* bias, void* out, int 
 FF_EXPORT int ff_scale(float* x, float a, size_t n, cudaStream_t stream) {
     if (n == 0) return 0;
     FF_LAUNCH(scale_kernel, (unsigned)((n + 255) / 256), 256, 0, stream, x, a, n);
+    FF_LAUNCH_CHECK();
+    return 0;
+}
+
+FF_EXPORT int ff_act_mul_table_rows(const void* g, const int* ids, const void* table, int table_cols, int col0, int vocab,
+                                    void* out, int dtype, int T, int n, int act, int* status, cudaStream_t stream) {
+    const size_t total = (size_t)T * n;
+    if (total == 0) return 0;
+    if (act < 0 || act > 1 || col0 < 0 || col0 + n > table_cols) return FF_ERR_BAD_ARG;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == 0)
+        FF_LAUNCH((act_mul_table_rows_kernel<float>), blocks, 256, 0, stream, (const float*)g, ids, (const float*)table,
+                  table_cols, col0, vocab, (float*)out, n, total, act, status);
+    else if (dtype == 1)
+        FF_LAUNCH((act_mul_table_rows_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)g, ids, (const bf16*)table,
+                  table_cols, col0, vocab, (bf16*)out, n, total, act, status);
+    else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;
 }

@@ -10,8 +10,9 @@
 // W_uv[h] out_latent[h].  This file finishes the query rows and writes the cache rows; the
 // attention itself is the paged attention the other mixers use.
 //
-// Rotation: the first rdims (<= rot_dim) elements of the rotated part, pairs (i, i + rdims/2), angle =
-// position * f_i; elements past rdims pass unchanged.  The angle is formed in double from
+// Rotation: the first rdims (<= rot_dim) elements of the rotated part, pairs (i, i + rdims/2) or, with
+// `interleaved`, (2i, 2i + 1), angle = position * f_i; elements past rdims pass unchanged.  A layer that reads
+// another layer's cache passes no down projection (`dkv` null): only its queries are finished.  The angle is formed in double from
 // the 64-bit frequency table and reduced there, so cos and sin are right to 32-bit rounding at
 // any position; norms and the rotation are 32-bit.
 #include "common.cuh"
@@ -20,14 +21,18 @@ namespace ff {
 
 template <typename T>
 __global__ void latent_finish_kernel(
-    const T* __restrict__ proj, int proj_stride, int q_off, int dkv_off,   // [T, ...]: q heads [H, dim + rot], dkv [kv_rank + rot]
+    const T* q_src, int q_stride,                                          // [T, ...]: q heads [H, dim + rot]
+    const T* dkv_src, int dkv_stride,                                      // [T, ...]: dkv [kv_rank + rot], or null
     const T* __restrict__ q_abs,                                          // [H, T, kv_rank]
     const float* __restrict__ c_norm_w, float eps, const double* __restrict__ freq /*[rot/2]*/,
     const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ block_table,
     int max_blocks, int block_size, int num_blocks, int planes, T* __restrict__ cache /*[blocks, planes, 1, block, d]*/,
     T* __restrict__ q_full /*[T, H, d]*/, int Ttot, int H, int dim, int rot, int rdims, int kv_rank,
-    int* __restrict__ status) {
+    int interleaved, int* __restrict__ status) {
     pdl_prologue();
+    q_src = pdl_fresh(q_src);
+    dkv_src = pdl_fresh(dkv_src);
+    q_abs = pdl_fresh(q_abs);
     extern __shared__ float sh[];           // cos[rdims/2], sin[rdims/2]
     __shared__ float scratch[32];
     const int t = blockIdx.x;
@@ -42,16 +47,19 @@ __global__ void latent_finish_kernel(
         s_cos[i] = (float)cs;
         s_sin[i] = (float)sn;
     }
-    const T* row = proj + (size_t)t * proj_stride;
-    const T* dkv = row + dkv_off;
+    // the partners of a pair: element `lo_of(i)` turns with element `hi_of(i)` by angle i
+    const int step = interleaved ? 2 : 1, gap = interleaved ? 1 : half;
+    const T* dkv = dkv_src ? dkv_src + (size_t)t * dkv_stride : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_float(dkv[i]); ss += v * v; }
+    if (dkv)
+        for (int i = threadIdx.x; i < kv_rank; i += blockDim.x) { const float v = to_float(dkv[i]); ss += v * v; }
     ss = block_sum(ss, scratch);             // also orders the writes of s_cos / s_sin before their use
     const float inv = 1.0f / sqrtf(ss / (float)kv_rank + eps);
     // the cache row
     const int seq = token_seq[t];
-    const int page = block_table[(size_t)seq * max_blocks + pos / block_size];
-    if (page < 0 || page >= num_blocks) {
+    const int page = dkv ? block_table[(size_t)seq * max_blocks + pos / block_size] : 0;
+    if (!dkv) {
+    } else if (page < 0 || page >= num_blocks) {
         if (threadIdx.x == 0) atomicExch(status, 2);
     } else {
         // one plane: the row is read as key and as value; two: the value plane repeats c, with zeros behind it
@@ -63,12 +71,13 @@ __global__ void latent_finish_kernel(
             if (vrow) vrow[i] = c;
         }
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
-            const float a = to_float(dkv[kv_rank + i]), b = to_float(dkv[kv_rank + half + i]);
-            krow[kv_rank + i] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
-            krow[kv_rank + half + i] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
+            const int e0 = kv_rank + i * step, e1 = e0 + gap;
+            const float a = to_float(dkv[e0]), b = to_float(dkv[e1]);
+            krow[e0] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
+            krow[e1] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
             if (vrow) {
-                vrow[kv_rank + i] = from_float<T>(0.f);
-                vrow[kv_rank + half + i] = from_float<T>(0.f);
+                vrow[e0] = from_float<T>(0.f);
+                vrow[e1] = from_float<T>(0.f);
             }
         }
         for (int i = threadIdx.x; i < rest; i += blockDim.x) {
@@ -82,13 +91,14 @@ __global__ void latent_finish_kernel(
         const int h = idx / kv_rank, i = idx - h * kv_rank;
         qf[(size_t)h * d + i] = q_abs[((size_t)h * Ttot + t) * kv_rank + i];
     }
-    const T* q = row + q_off;
+    const T* q = q_src + (size_t)t * q_stride;
     for (int idx = threadIdx.x; idx < H * half; idx += blockDim.x) {
         const int h = idx / half, i = idx - h * half;
         const T* qr = q + (size_t)h * (dim + rot) + dim;
-        const float a = to_float(qr[i]), b = to_float(qr[half + i]);
-        qf[(size_t)h * d + kv_rank + i] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
-        qf[(size_t)h * d + kv_rank + half + i] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
+        const int e0 = i * step, e1 = e0 + gap;
+        const float a = to_float(qr[e0]), b = to_float(qr[e1]);
+        qf[(size_t)h * d + kv_rank + e0] = from_float<T>(a * s_cos[i] - b * s_sin[i]);
+        qf[(size_t)h * d + kv_rank + e1] = from_float<T>(b * s_cos[i] + a * s_sin[i]);
     }
     for (int idx = threadIdx.x; idx < H * rest; idx += blockDim.x) {
         const int h = idx / rest, i = idx - h * rest;
@@ -96,18 +106,20 @@ __global__ void latent_finish_kernel(
     }
 }
 
-// y[t, h * vdim + j] = val[h, t, j] * sigmoid(g[t, h * vdim + j])
+// y[t, h * vdim + j] = val[h, t, j] * sigmoid(g[t, h * vdim + j]), or, with one gate a head, sigmoid(g[t, h])
 template <typename T>
-__global__ void latent_gate_kernel(const T* __restrict__ val /*[H,T,vdim]*/, const T* __restrict__ g, int g_stride,
-                                   T* __restrict__ y, int Ttot, int H, int vdim, size_t total) {
+__global__ void latent_gate_kernel(const T* val /*[H,T,vdim]*/, const T* g, int g_stride,
+                                   T* __restrict__ y, int Ttot, int H, int vdim, size_t total, int per_head) {
     pdl_prologue();
+    val = pdl_fresh(val);
+    g = pdl_fresh(g);
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= total) return;
     const int hv = H * vdim;
     const size_t t = idx / hv;
     const int c = (int)(idx - t * hv);
     const int h = c / vdim, j = c - h * vdim;
-    const float gv = to_float(g[t * g_stride + c]);
+    const float gv = to_float(g[t * g_stride + (per_head ? h : c)]);
     y[idx] = from_float<T>(to_float(val[((size_t)h * Ttot + t) * vdim + j]) / (1.0f + expf(-gv)));
 }
 
@@ -115,40 +127,40 @@ __global__ void latent_gate_kernel(const T* __restrict__ val /*[H,T,vdim]*/, con
 
 using namespace ff;
 
-FF_EXPORT int ff_latent_finish(const void* proj, int dtype, int proj_stride, int q_off, int dkv_off, const void* q_abs,
+FF_EXPORT int ff_latent_finish(const void* q, int q_stride, const void* dkv, int dkv_stride, int dtype, const void* q_abs,
                                const float* c_norm_w, float eps, const double* freq, const int* positions,
                                const int* token_seq, const int* block_table, int max_blocks, int block_size,
                                int num_blocks, int planes, void* cache, void* q_full, int T, int H, int dim, int rot,
-                               int rdims, int kv_rank, int* status, cudaStream_t stream) {
+                               int rdims, int kv_rank, int interleaved, int* status, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (planes != 1 && planes != 2) return FF_ERR_BAD_ARG;
     if (rot < 0 || rdims < 0 || rdims > rot || rdims % 2 || kv_rank <= 0) return FF_ERR_BAD_ARG;
     const size_t smem = (size_t)(rdims > 0 ? rdims : 2) * sizeof(float);
     if (smem > 40 * 1024) return FF_ERR_UNSUPPORTED;
     if (dtype == 0)
-        FF_LAUNCH((latent_finish_kernel<float>), T, 256, smem, stream, (const float*)proj, proj_stride, q_off, dkv_off,
+        FF_LAUNCH((latent_finish_kernel<float>), T, 256, smem, stream, (const float*)q, q_stride, (const float*)dkv, dkv_stride,
                   (const float*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, planes, (float*)cache, (float*)q_full, T, H, dim, rot, rdims, kv_rank, status);
+                  num_blocks, planes, (float*)cache, (float*)q_full, T, H, dim, rot, rdims, kv_rank, interleaved, status);
     else if (dtype == 1)
-        FF_LAUNCH((latent_finish_kernel<bf16>), T, 256, smem, stream, (const bf16*)proj, proj_stride, q_off, dkv_off,
+        FF_LAUNCH((latent_finish_kernel<bf16>), T, 256, smem, stream, (const bf16*)q, q_stride, (const bf16*)dkv, dkv_stride,
                   (const bf16*)q_abs, c_norm_w, eps, freq, positions, token_seq, block_table, max_blocks, block_size,
-                  num_blocks, planes, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, rdims, kv_rank, status);
+                  num_blocks, planes, (bf16*)cache, (bf16*)q_full, T, H, dim, rot, rdims, kv_rank, interleaved, status);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;
 }
 
 FF_EXPORT int ff_latent_gate(const void* val, const void* g, int g_stride, int dtype, void* y, int T, int H, int vdim,
-                             cudaStream_t stream) {
+                             int per_head, cudaStream_t stream) {
     const size_t total = (size_t)T * H * vdim;
     if (total == 0) return 0;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0)
         FF_LAUNCH((latent_gate_kernel<float>), blocks, 256, 0, stream, (const float*)val, (const float*)g, g_stride,
-                  (float*)y, T, H, vdim, total);
+                  (float*)y, T, H, vdim, total, per_head);
     else if (dtype == 1)
         FF_LAUNCH((latent_gate_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)val, (const bf16*)g, g_stride,
-                  (bf16*)y, T, H, vdim, total);
+                  (bf16*)y, T, H, vdim, total, per_head);
     else return FF_ERR_BAD_ARG;
     FF_LAUNCH_CHECK();
     return 0;

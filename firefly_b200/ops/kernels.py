@@ -233,11 +233,12 @@ def _check_dist_bias(dist_bias: Optional[torch.Tensor], nq: int, window: int) ->
 def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, block_table: torch.Tensor,
                          token_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                          nq: int, nkv: int, d: int, scale: float, window: int,
-                         status: torch.Tensor, dist_bias: Optional[torch.Tensor] = None) -> None:
+                         status: torch.Tensor, dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Attention of every query token over its sequence's cached keys 0..pos
     (or the last ``window`` of them; 0 = all).  ``q`` is read with row stride
     ``q_stride`` elements (it may be the head of a wider qkv buffer).  ``dist_bias`` float32 [nq, L]:
-    entry (h, i - j) is taken off the score of query position i and key position j."""
+    entry (h, i - j) is taken off the score of query position i and key position j.  ``softcap`` c > 0: the scaled score
+    s becomes c tanh(s / c) (before the bias)."""
     _need_cuda(cache, block_table, token_seq, positions, out, status, dist_bias)
     _check_dist_bias(dist_bias, nq, window)
     if not q.is_cuda:
@@ -250,7 +251,7 @@ def paged_attention_simt(q: torch.Tensor, q_stride: int, cache: torch.Tensor, bl
         _p(q), c_int(_dt(q)), c_int(q_stride), _p(cache), _p(block_table), c_int(block_table.shape[1]),
         _p(token_seq), _p(positions), _p(out), c_int(out.shape[1]), c_int(T), c_int(nq), c_int(nkv),
         c_int(d), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(dist_bias),
-        c_int(dist_bias.shape[1] if dist_bias is not None else 0), _p(status), _stream()), "paged_attention_simt")
+        c_int(dist_bias.shape[1] if dist_bias is not None else 0), c_float(softcap), _p(status), _stream()), "paged_attention_simt")
 
 
 _sample_scratch = {}
@@ -486,7 +487,8 @@ def _bias_args(dist_bias: Optional[torch.Tensor], nq: int, window: int):
 
 
 def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale,
-               window, status: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None) -> None:
+               window, status: Optional[torch.Tensor] = None, dist_bias: Optional[torch.Tensor] = None,
+               softcap: float = 0.0) -> None:
     """Tensor-core attention for any mix of sequences (bfloat16).  ``status`` (int32 [1]) is set to 4
     when a key that must be read has no valid page in the block table.  ``dist_bias``: as for
     `paged_attention_simt`."""
@@ -496,12 +498,12 @@ def attn_tiled(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, o
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), *_bias_args(dist_bias, nq, window),
-        _p(status), _stream()), "attn_tiled")
+        c_float(softcap), _p(status), _stream()), "attn_tiled")
 
 
 def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, nq, nkv, d,
                 scale, window, num_splits, status: Optional[torch.Tensor] = None,
-                dist_bias: Optional[torch.Tensor] = None) -> None:
+                dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Split-KV tensor-core attention when every sequence has one token (bfloat16).  ``status`` and
     ``dist_bias`` as for `attn_tiled`."""
     _need_cuda(pages, table, cu_q, ctx_lens, out, part_o, part_ml, status, dist_bias)
@@ -510,7 +512,7 @@ def attn_decode(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, 
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(num_splits),
-        *_bias_args(dist_bias, nq, window), _p(status), _stream()), "attn_decode")
+        *_bias_args(dist_bias, nq, window), c_float(softcap), _p(status), _stream()), "attn_decode")
     global LAUNCHES
     if num_splits > 1:
         LAUNCHES += 1     # the kernel that joins the splits
@@ -572,7 +574,8 @@ def tc_attention_supported(dtype: torch.dtype, d: int, block_size: int, max_kv_l
 
 
 def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out, nq, nkv, d, scale, window,
-            status, page_list: Optional[int] = None, shares=None, dist_bias: Optional[torch.Tensor] = None) -> None:
+            status, page_list: Optional[int] = None, shares=None, dist_bias: Optional[torch.Tensor] = None,
+            softcap: float = 0.0) -> None:
     """tcgen05 flash attention over the paged cache (bfloat16); total_tiles counts row tiles of 128.
     ``shares`` = (count, part_o, part_ml, first row, rows): every row tile's keys are shared out over
     ``count`` blocks and a second kernel joins their partial results (for prompts so short that their
@@ -589,7 +592,7 @@ def attn_tc(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, total_tiles, out,
         _p(q), c_int(q_stride), _p(pages), _p(table), c_int(table.shape[1]), _p(cu_q), _p(ctx_lens),
         c_int(n_seqs), c_int(total_tiles), _p(out), c_int(out.shape[1]), c_int(nq), c_int(nkv),
         c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), _p(status), c_int(count), _p(part_o),
-        _p(part_ml), c_int(row0), c_int(rows), *_bias_args(dist_bias, nq, window), _stream()), "attn_tc")
+        _p(part_ml), c_int(row0), c_int(rows), *_bias_args(dist_bias, nq, window), c_float(softcap), _stream()), "attn_tc")
     if count > 1:
         global LAUNCHES
         LAUNCHES += 1     # the kernel that joins the shares
@@ -672,7 +675,7 @@ def _decode_scratch(ws, n: int, nq: int, nkv: int, d: int, splits: int):
 
 def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, part_o, part_ml, seq_ranges,
                       nq, nkv, d, scale, window, units, max_ranges, heads=None, status=None,
-                      dist_bias: Optional[torch.Tensor] = None) -> None:
+                      dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Split-KV decode attention with `units` blocks per kv head shared out among the sequences
     in proportion to their lengths.  ``heads = (q_norm_w, k_norm_w, eps, cos_sin)``: q is the raw
     q|k|v projection and the kernel finishes the heads itself."""
@@ -686,8 +689,8 @@ def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, pa
         c_int(n_seqs), _p(out), c_int(out.shape[1]), _p(part_o), _p(part_ml), _p(seq_ranges), c_int(nq),
         c_int(nkv), c_int(block_size), c_int(num_blocks), c_float(scale), c_int(window), c_int(units),
         c_int(max_ranges), c_int(1 if heads is not None else 0), _p(qw), _p(kw), c_float(eps), _p(cos_sin),
-        c_int(cos_sin.shape[0] if cos_sin is not None else 0), *_bias_args(dist_bias, nq, window), _p(status),
-        _stream()), "attn_decode_units")
+        c_int(cos_sin.shape[0] if cos_sin is not None else 0), *_bias_args(dist_bias, nq, window), c_float(softcap),
+        _p(status), _stream()), "attn_decode_units")
     global LAUNCHES, BY_LENGTH_CALLS
     BY_LENGTH_CALLS += 1
     if units > n_seqs and max_ranges > 1:
@@ -696,14 +699,15 @@ def attn_decode_units(q, q_stride, pages, table, cu_q, ctx_lens, n_seqs, out, pa
 
 def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: torch.Tensor, ctx,
                     out: torch.Tensor, nq: int, nkv: int, d: int, scale: float, window: int,
-                    dist_bias: Optional[torch.Tensor] = None) -> None:
+                    dist_bias: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Attention of a step's tokens over the paged cache; picks the kernel: the
     tensor-core kernels for bfloat16 and head sizes in steps of 16, the plain
     kernel for 32-bit and every other head size up to 256.  ``dist_bias`` float32 [nq, L >= window]: entry
-    (h, i - j) is taken off the score of query position i and key position j."""
+    (h, i - j) is taken off the score of query position i and key position j.  ``softcap`` c > 0: the scaled score s
+    becomes c tanh(s / c), before the bias."""
     if _ATTN_FORCE_SIMT or not mma_attention_supported(q.dtype, d):
         paged_attention_simt(q, q_stride, pages, table, ctx.token_seq, ctx.positions, out, nq, nkv, d,
-                             scale, window, ctx.status, dist_bias)
+                             scale, window, ctx.status, dist_bias, softcap)
         return
     G = nq // nkv
     n = ctx.num_seqs
@@ -716,10 +720,10 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
         if units:
             attn_decode_units(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml,
                               seq_ranges, nq, nkv, d, scale, window, units, DECODE_MAX_RANGES, status=ctx.status,
-                              dist_bias=dist_bias)
+                              dist_bias=dist_bias, softcap=softcap)
         else:
             attn_decode(q, q_stride, pages, table, ctx.cu_q, ctx.ctx_lens, n_dec, out, part_o, part_ml, nq, nkv,
-                        d, scale, window, splits, ctx.status, dist_bias)
+                        d, scale, window, splits, ctx.status, dist_bias, softcap)
     if n_dec < n:
         # portions of prompts: tiled kernel over the remaining sequences (token offsets in cu_q are absolute)
         # every layer of a step asks the same of the step's arrays: worked out once and kept with the step
@@ -748,11 +752,11 @@ def paged_attention(q: torch.Tensor, q_stride: int, pages: torch.Tensor, table: 
                 shares = (count, ctx.workspace.get("attn.tc_part_o", (cells * d,), torch.float32),
                           ctx.workspace.get("attn.tc_part_ml", (cells * 2,), torch.float32), row0, rows)
             attn_tc(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec, tiles,
-                    out, nq, nkv, d, scale, window, ctx.status, shares=shares, dist_bias=dist_bias)
+                    out, nq, nkv, d, scale, window, ctx.status, shares=shares, dist_bias=dist_bias, softcap=softcap)
         else:
             tiles = sum(-(-(ql * G) // 64) for ql in ctx.q_lens[n_dec:])
             attn_tiled(q, q_stride, pages, table_t, cu_q_t, ctx_lens_t, n - n_dec,
-                       tiles, out, nq, nkv, d, scale, window, ctx.status, dist_bias)
+                       tiles, out, nq, nkv, d, scale, window, ctx.status, dist_bias, softcap)
 
 
 # --------------------------------------------------------------------------- #
@@ -880,36 +884,47 @@ def wkv_out(o, gate, norm_w, eps: float, y, heads: int, dim: int) -> None:
 
 # --------------------------------------------------------------------------- #
 # attention over a cached latent vector (csrc/latent_attention.cu)
-def latent_finish(proj, q_off: int, dkv_off: int, q_abs, c_norm_w, eps: float, freq, ctx, table, pages, q_full,
-                  heads: int, dim: int, rot: int, kv_rank: int, rotary_dims: Optional[int] = None) -> None:
-    """Finish a step's query rows and write its cache rows.  proj [T, *] holds the q heads ([heads, dim + rot]
-    from column q_off) and the down projection ([kv_rank + rot] from column dkv_off); q_abs [heads, T, kv_rank];
-    freq float64 [rotary_dims/2] (rotary_dims <= rot, by default rot: the first that many elements of the rotated
-    part turn, the rest pass); pages [blocks, 2, 1, block, kv_rank + rot]; q_full [T, heads * (kv_rank + rot)]."""
+def latent_finish(q, dkv, q_abs, c_norm_w, eps: float, freq, ctx, table, pages, q_full,
+                  heads: int, dim: int, rot: int, kv_rank: int, rotary_dims: Optional[int] = None,
+                  interleaved: bool = False) -> None:
+    """Finish a step's query rows and write its cache rows.  ``q`` [T, heads * (dim + rot)] and ``dkv`` [T, kv_rank +
+    rot] (the down projection; None: the layer reads a cache that another layer writes, only the queries are
+    finished) may be column ranges of wider matrices; q_abs [heads, T, kv_rank]; freq float64 [rotary_dims/2]
+    (rotary_dims <= rot, by default rot: the first that many elements of the rotated part turn, the rest pass;
+    ``interleaved``: element 2i turns with element 2i + 1, else i with i + rotary_dims/2);
+    pages [blocks, planes, 1, block, kv_rank + rot]; q_full [T, heads * (kv_rank + rot)]."""
     rdims = rot if rotary_dims is None else int(rotary_dims)
-    _need_cuda(proj, q_abs, c_norm_w, freq, table, pages, q_full)
-    T = proj.shape[0]
+    _need_cuda(q_abs, c_norm_w, freq, table, pages, q_full)
+    for m in (q, dkv):
+        if m is not None and (not m.is_cuda or m.stride(1) != 1):
+            raise KernelError("latent_finish: q and dkv are CUDA matrices with contiguous rows")
+    T = q.shape[0]
     d = kv_rank + rot
     num_blocks, planes, one, block_size, cd = pages.shape
-    assert planes in (1, 2) and one == 1 and cd == d and pages.dtype == proj.dtype == q_abs.dtype == q_full.dtype
+    assert planes in (1, 2) and one == 1 and cd == d and pages.dtype == q.dtype == q_abs.dtype == q_full.dtype
+    assert q.shape[1] == heads * (dim + rot) and (dkv is None or (dkv.shape == (T, d) and dkv.dtype == q.dtype))
     assert q_abs.shape == (heads, T, kv_rank) and q_full.shape == (T, heads * d)
     assert freq.dtype == torch.float64 and freq.numel() == rdims // 2 and c_norm_w.dtype == torch.float32
     _check(_lib("latent_attention").ff_latent_finish(
-        _p(proj), c_int(_dt(proj)), c_int(proj.stride(0)), c_int(q_off), c_int(dkv_off), _p(q_abs), _p(c_norm_w),
+        c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(dkv.data_ptr() if dkv is not None else None),
+        c_int(dkv.stride(0) if dkv is not None else 0), c_int(_dt(q)), _p(q_abs), _p(c_norm_w),
         c_float(eps), _p(freq), _p(ctx.positions), _p(ctx.token_seq), _p(table), c_int(table.shape[1]),
         c_int(block_size), c_int(num_blocks), c_int(planes), _p(pages), _p(q_full), c_int(T), c_int(heads), c_int(dim),
-        c_int(rot), c_int(rdims), c_int(kv_rank), _p(ctx.status), _stream()), "latent_finish")
+        c_int(rot), c_int(rdims), c_int(kv_rank), c_int(1 if interleaved else 0), _p(ctx.status), _stream()), "latent_finish")
 
 
-def latent_gate(val, g, y, heads: int, vdim: int) -> None:
-    """y[t, h*vdim + j] = val[h, t, j] * sigmoid(g[t, h*vdim + j]); g may be a column range of a wider matrix."""
+def latent_gate(val, g, y, heads: int, vdim: int, per_head: bool = False) -> None:
+    """y[t, h*vdim + j] = val[h, t, j] * sigmoid(g[t, h*vdim + j]) (``per_head``: sigmoid(g[t, h])); g may be a column
+    range of a wider matrix."""
     if not g.is_cuda or g.stride(1) != 1:
         raise KernelError("latent_gate: the gate must be a CUDA matrix with contiguous rows")
     _need_cuda(val, y)
     T = y.shape[0]
     assert val.shape == (heads, T, vdim) and y.shape == (T, heads * vdim) and val.dtype == g.dtype == y.dtype
+    assert g.shape[1] == (heads if per_head else heads * vdim)
     _check(_lib("latent_attention").ff_latent_gate(_p(val), c_void_p(g.data_ptr()), c_int(g.stride(0)), c_int(_dt(y)),
-                                                  _p(y), c_int(T), c_int(heads), c_int(vdim), _stream()), "latent_gate")
+                                                  _p(y), c_int(T), c_int(heads), c_int(vdim),
+                                                  c_int(1 if per_head else 0), _stream()), "latent_gate")
 
 
 # --------------------------------------------------------------------------- #
@@ -1034,6 +1049,18 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str, bias: Opt
                                          c_int(GLU_ACTIVATIONS[activation]), c_float(limit), _stream()), "glu_act")
 
 
+def act_mul_table_rows(g: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, col0: int, out: torch.Tensor,
+                       activation: str, status: torch.Tensor) -> None:
+    """out[t, j] = act(g[t, j]) * table[ids[t], col0 + j] for the n columns of ``g``; act "silu" or "gelu_tanh"."""
+    _need_cuda(g, ids, table, out, status)
+    T, n = g.shape
+    assert g.dtype == table.dtype == out.dtype and out.shape == g.shape and g.is_contiguous() and out.is_contiguous()
+    assert ids.dtype == torch.int32 and ids.numel() == T and table.is_contiguous() and col0 + n <= table.shape[1]
+    _check(_lib("elementwise").ff_act_mul_table_rows(
+        _p(g), _p(ids), _p(table), c_int(table.shape[1]), c_int(col0), c_int(table.shape[0]), _p(out), c_int(_dt(out)),
+        c_int(T), c_int(n), c_int({"silu": 0, "gelu_tanh": 1}[activation]), _p(status), _stream()), "act_mul_table_rows")
+
+
 def scale_(x: torch.Tensor, a: float) -> None:
     """x *= a for a contiguous float32 tensor."""
     _need_cuda(x)
@@ -1042,12 +1069,16 @@ def scale_(x: torch.Tensor, a: float) -> None:
 
 
 def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim: int, eps: float, freq: torch.Tensor,
-                         mag: float, ctx, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor]) -> None:
+                         mag: float, ctx, block_table: Optional[torch.Tensor], cache: Optional[torch.Tensor], *,
+                         interleaved: bool = False, normalize: bool = True, bias: Optional[torch.Tensor] = None) -> None:
     """Heads whose unit norm comes behind the rotation: q and k heads of ``qkv`` [T, (nq + 2 nkv) d] are turned
     (their first 2 * len(freq) elements; cos and sin times ``mag``), divided by their root mean square over
     ``norm_dim`` elements, q written back in place, k and v into the paged cache [blocks, 2, nkv, block, d].
-    ``nkv == 0``: q only."""
-    _need_cuda(qkv, freq, block_table, cache)
+    ``nkv == 0``: q only.  ``interleaved``: element 2i turns with element 2i + 1 (else i with i + len(freq));
+    ``normalize`` False: no unit norm; ``bias`` float32 [(nq + 2 nkv) d]: added to q, k and v first, in 32-bit."""
+    _need_cuda(qkv, freq, block_table, cache, bias)
+    if bias is not None:
+        assert bias.dtype == torch.float32 and bias.numel() == (nq + 2 * nkv) * d and bias.is_contiguous()
     T, width = qkv.shape
     assert freq.dtype == torch.float64 and width == (nq + 2 * nkv) * d
     if nkv:
@@ -1059,7 +1090,8 @@ def rope_unit_norm_store(qkv: torch.Tensor, nq: int, nkv: int, d: int, norm_dim:
     _check(_lib("head_finish").ff_rope_unit_norm_store(
         _p(qkv), c_int(_dt(qkv)), c_int(width), c_int(T), c_int(nq), c_int(nkv), c_int(d), c_int(norm_dim), c_float(eps),
         _p(freq), c_int(2 * freq.numel()), c_float(mag), _p(ctx.positions), _p(ctx.token_seq), _p(block_table),
-        c_int(max_blocks), c_int(block_size), c_int(num_blocks), _p(cache), _p(ctx.status), _stream()),
+        c_int(max_blocks), c_int(block_size), c_int(num_blocks), _p(cache), _p(ctx.status),
+        c_int(1 if interleaved else 0), c_int(1 if normalize else 0), _p(bias), _stream()),
         "rope_unit_norm_store")
 
 
@@ -1235,37 +1267,41 @@ def delta_state_floats(heads: int, N: int, V: int) -> int:
 
 def delta_rule_scan(q, k, v, beta, a, dt_bias: torch.Tensor, a_log: torch.Tensor, state: torch.Tensor, state_off: int,
                     ctx, o: torch.Tensor, heads: int, N: int, V: int, *, heads_per_group: int = 1, q_scale: float = 1.0,
-                    unit_eps: float = 1e-6) -> None:
+                    unit_eps: float = 1e-6, decay_per_head: bool = False) -> None:
     """S = diag(g) S; u = beta (v - S^T k); S += k u^T; o = S^T q per head, token by token.  ``q``, ``k``, ``v``,
     ``beta``, ``a``: (matrix [T, *], first column); a q/k row holds [groups, N] (made unit vectors here, q also times
     ``q_scale``), a v row [heads, V], a beta row [heads] (its sigmoid is taken here), an ``a`` row float32
-    [heads, N] with g = exp(-exp(a_log) softplus(a + dt_bias)).  ``state`` float32 [slots, *]: `delta_state_floats`
+    [heads, N] with g = exp(-exp(a_log) softplus(a + dt_bias)) (``decay_per_head``: an ``a`` row is [heads], dt_bias
+    [heads], and a head's key channels all decay alike).  ``state`` float32 [slots, *]: `delta_state_floats`
     floats from ``state_off``; o float32 [T, heads * V]."""
     (qm, q0), (km, k0), (vm, v0), (bm, b0), (am, a0) = q, k, v, beta, a
     _need_cuda(qm, km, vm, bm, am, dt_bias, a_log, state, o)
     T = o.shape[0]
     assert qm.dtype == km.dtype == vm.dtype == bm.dtype and am.dtype == torch.float32
     assert all(m.stride(1) == 1 for m in (qm, km, vm, bm, am))
-    assert dt_bias.dtype == a_log.dtype == torch.float32 and dt_bias.numel() == heads * N and a_log.numel() == heads
+    assert dt_bias.dtype == a_log.dtype == torch.float32 and a_log.numel() == heads
+    assert dt_bias.numel() == (heads if decay_per_head else heads * N)
     assert o.dtype == torch.float32 and o.shape == (T, heads * V) and state.dtype == torch.float32
     _check(_lib("delta_rule").ff_delta_rule_scan(
         _p(qm), c_int(qm.stride(0)), c_int(q0), _p(km), c_int(km.stride(0)), c_int(k0), _p(vm), c_int(vm.stride(0)),
         c_int(v0), _p(bm), c_int(bm.stride(0)), c_int(b0), c_int(_dt(qm)), _p(am), c_int(am.stride(0)), c_int(a0),
-        _p(dt_bias), _p(a_log), c_int(heads_per_group), c_float(q_scale), c_float(unit_eps), _p(state),
+        _p(dt_bias), _p(a_log), c_int(1 if decay_per_head else 0), c_int(heads_per_group), c_float(q_scale), c_float(unit_eps), _p(state),
         ctypes.c_longlong(state.stride(0)), c_int(state_off), _p(ctx.cu_q), _p(ctx.state_slots), _p(ctx.seq_fresh),
         _p(o), c_int(T), c_int(ctx.num_seqs), c_int(heads), c_int(N), c_int(V), _stream()), "delta_rule_scan")
 
 
-def head_norm_gate(o: torch.Tensor, gate, weight: torch.Tensor, eps: float, y: torch.Tensor, heads: int, V: int) -> None:
-    """y[t, h, :] = rms_norm(o[t, h, :]) * weight * sigmoid(g[t, h, :]): the norm over each head's V values, one weight
-    row [V] for all heads; ``gate`` = (float32 matrix, first column)."""
+def head_norm_gate(o: torch.Tensor, gate, weight: torch.Tensor, eps: float, y: torch.Tensor, heads: int, V: int,
+                   gate_activation: str = "sigmoid") -> None:
+    """y[t, h, :] = rms_norm(o[t, h, :]) * weight * act(g[t, h, :]): the norm over each head's V values, one weight
+    row [V] for all heads; ``gate`` = (float32 matrix, first column); act = "sigmoid" or "silu"."""
     gm, g0 = gate
     _need_cuda(o, gm, weight, y)
     T = o.shape[0]
     assert o.dtype == gm.dtype == weight.dtype == torch.float32 and weight.numel() == V and gm.stride(1) == 1
     assert o.shape == (T, heads * V) and y.shape == o.shape and o.is_contiguous() and y.is_contiguous()
     _check(_lib("delta_rule").ff_head_norm_gate(_p(o), _p(gm), c_int(gm.stride(0)), c_int(g0), _p(weight), c_float(eps),
-                                               _p(y), c_int(_dt(y)), c_int(T), c_int(heads), c_int(V), _stream()),
+                                               _p(y), c_int(_dt(y)), c_int(T), c_int(heads), c_int(V),
+                                               c_int({"sigmoid": 0, "silu": 1}[gate_activation]), _stream()),
            "head_norm_gate")
 
 

@@ -29,6 +29,11 @@ Further parameters, for designs that differ from the above (defaults: as above):
                     qk_norm_eps) behind the rotation instead of a weighted norm in front of it; the rotation may
                     cover only the head's first elements and be rescaled (``position``'s parameters)
     q_leaf, k_leaf, v_leaf, o_leaf   the tensors' leaves under the prefix
+    bias_suffix     q, k and v have biases (the tensor's leaf + this suffix), added in 32-bit by the kernel that
+                    finishes the heads
+    softcap         c > 0: the scaled score s becomes c tanh(s / c)
+A position part whose ``pairing`` is "interleaved" (element 2i turns with element 2i + 1) is served by the same
+head-finishing kernel as the unit norm, which forms the angles itself from the frequencies.
 """
 from __future__ import annotations
 
@@ -71,6 +76,19 @@ class GQAttention(Part):
         self.chunk = self.p("chunk", None)
         self.unit_norm = bool(self.p("unit_norm_after_rotation", False))
         self.leaf = {k: self.p(k + "_leaf", k + "_proj.weight") for k in "qkvo"}
+        self.bias_suffix = self.p("bias_suffix", None)
+        self.softcap = float(self.p("softcap", 0.0) or 0.0)
+        if self.softcap < 0:
+            raise ValueError("softcap must be positive (or absent)")
+        interleaved = getattr(position, "pairing", "half") == "interleaved"
+        # the kernel that forms the angles from the frequencies also adds biases and takes either pairing
+        self.by_frequencies = self.unit_norm or interleaved or self.bias_suffix is not None
+        if self.by_frequencies and self.qk_norm:
+            raise ValueError("qk_norm (in front of the rotation) excludes biases, the interleaved pairing and the unit norm")
+        if self.by_frequencies and position is not None and not hasattr(position, "frequencies"):
+            raise ValueError("this attention needs a position encoding that gives its frequencies")
+        self.interleaved = interleaved
+        self.bias = None
         if self.chunk is not None and (self.window is not None or int(self.chunk) <= 0):
             raise ValueError("chunk must be positive and excludes window")
         if self.unit_norm and self.qk_norm:
@@ -98,6 +116,12 @@ class GQAttention(Part):
             out += [WeightSpec(self.name(L["k"]), (self.nkv * self.dk, self.hidden)),
                     WeightSpec(self.name(L["v"]), (self.nkv * self.dv, self.hidden))]
         out.append(WeightSpec(self.name(L["o"]), (self.hidden, self.nq * self.dv)))
+        if self.bias_suffix is not None:
+            sfx = self.bias_suffix
+            out.append(WeightSpec(self.name(L["q"]) + sfx, (self.nq * self.dk,), init="zeros", as_float32=True))
+            if self.has_kv:
+                out += [WeightSpec(self.name(L["k"]) + sfx, (self.nkv * self.dk,), init="zeros", as_float32=True),
+                        WeightSpec(self.name(L["v"]) + sfx, (self.nkv * self.dv,), init="zeros", as_float32=True)]
         if self.qk_norm:
             out.append(WeightSpec(self.name("q_norm.weight"), (self.d,), init="norm", as_float32=True))
             if self.has_kv:
@@ -139,6 +163,18 @@ class GQAttention(Part):
             wo = torch.zeros((self.hidden, self.nq, self.d), dtype=self.w_o.dtype, device=self.w_o.device)
             wo[:, :, : self.dv] = self.w_o.view(self.hidden, self.nq, self.dv)
             self.w_o = wo.view(self.hidden, self.nq * self.d).contiguous()
+        if self.bias_suffix is not None:       # one row in the projection's layout, heads filled up with zeros
+            sfx = self.bias_suffix
+            parts = [(self.leaf["q"], self.nq, self.dk)]
+            if self.has_kv:
+                parts += [(self.leaf["k"], self.nkv, self.dk), (self.leaf["v"], self.nkv, self.dv)]
+            rows = []
+            for leaf, heads, size in parts:
+                b = self._vector32(tensors[self.name(leaf) + sfx]).view(heads, size)
+                full = torch.zeros((heads, self.d), dtype=torch.float32, device=b.device)
+                full[:, :size] = b
+                rows.append(full.view(-1))
+            self.bias = torch.cat(rows).contiguous()
         if self.qk_norm:
             self.q_norm_w = self._vector32(tensors[self.name("q_norm.weight")])
             if self.has_kv:
@@ -163,18 +199,20 @@ class GQAttention(Part):
         qkv = ws.get("attn.qkv", (T, width), ctx.dtype)
         apply_linear(x, w, qkv, ctx, "attn.qkv")
         pages, table = ctx.kv(slot)
-        rot = self.position.rotary_table() if self.position is not None and not self.unit_norm else None
+        rot = self.position.rotary_table() if self.position is not None and not self.by_frequencies else None
         cos_sin, rotary_dim = rot if rot is not None else (None, 0)
         att = ws.get("attn.out", (T, self.nq * self.d), ctx.dtype)
-        if self.unit_norm:
+        if self.by_frequencies:
             if self.position is not None:
                 freq, mag = self.position.frequencies(), self.position.magnitude
             else:
                 freq, mag = ctx.workspace.get("attn.no_freq", (0,), torch.float64), 1.0
+            bias = self.bias if (self.bias is None or write_cache or not self.has_kv) else self.bias[: self.nq * self.d]
             K.rope_unit_norm_store(qkv, self.nq, nkv_w, self.d, self.dk, self.eps, freq, mag, ctx,
-                                   table if write_cache else None, pages if write_cache else None)
+                                   table if write_cache else None, pages if write_cache else None,
+                                   interleaved=self.interleaved, normalize=self.unit_norm, bias=bias)
             self._attend(qkv, width, pages, table, ctx, att)
-        elif write_cache and self.chunk is None and K.decode_finishes_heads(ctx, ctx.dtype, self.nq, self.nkv, self.d, rotary_dim):
+        elif write_cache and self.chunk is None and not self.softcap and K.decode_finishes_heads(ctx, ctx.dtype, self.nq, self.nkv, self.d, rotary_dim):
             # a step of single tokens: the attention kernel finishes the heads itself
             K.attn_decode_heads(qkv, pages, table, ctx, att, self.nq, self.nkv, self.d, self.scale,
                                 0 if self.window is None else int(self.window), self.q_norm_w,
@@ -191,7 +229,7 @@ class GQAttention(Part):
 
     def _attend(self, qkv, width, pages, table, ctx, att) -> None:
         K.paged_attention(qkv, width, pages, table, ctx, att, self.nq, self.nkv, self.d, self.scale,
-                          self._mask())
+                          self._mask(), softcap=self.softcap)
 
 
 register_part("mixer", "gqa_attention", GQAttention)

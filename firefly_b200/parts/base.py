@@ -25,6 +25,8 @@ Categories and what each must offer (beyond ``weight_specs`` and ``bind``):
 * ``filter``        sits between a block's first norm and its mixer: ``cache_spec()`` -> StateSpec | None,
                     ``wants_float32_input`` (bool) and ``forward(x, ctx, slot) -> x'`` [T, hidden] in the
                     activation type.  A block that holds one keeps its state under a cache id of its own.
+* ``tail``          runs at the end of a block, behind the feed-forward, on the stream itself:
+                    ``forward(residual, pending, ctx) -> (residual, pending)`` (it adds ``pending`` in first).
 * ``embedding``     ``forward(ctx) -> residual`` float32 [T, hidden].
 * ``head``          ``forward(x_rows) -> logits`` float32 [rows, vocab].
 
@@ -68,7 +70,7 @@ import torch
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightSpec
 
-CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "junction", "filter")
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "arrangement", "embedding", "head", "junction", "filter", "tail")
 _REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in CATEGORIES}
 
 

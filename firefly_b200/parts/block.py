@@ -6,6 +6,8 @@ A block may hold an *input filter* (``LayerSpec.params["input_filter"]``, a Part
 the mixer reads is then filter(norm_0(h)), e.g. a short causal convolution over time added to its own input.  The
 filter's state lives under a cache id of its own per run (``cache.spec.filter_slot``).  A ``pre_norm`` block without
 a feed-forward ends after the mixer.
+A block may also hold a *tail* (``LayerSpec.params["tail"]``, a PartSpec of category ``tail``): a part that runs at the
+block's end on the stream itself, e.g. an input that the token brings to every layer.
 The residual stream ``h`` is 32-bit.  A part's output is not added at once: it is
 handed on as ``pending`` and the next norm adds it while it reads the row, so
 each sum is done once, in 32-bit, without a pass of its own.
@@ -25,6 +27,7 @@ class Block:
     """Base of arrangements: owns the built parts of one layer."""
 
     n_norms = 2
+    runs_tail = False            # an arrangement that runs ``params["tail"]`` at its end sets this
 
     def __init__(self, layer_spec, rt: Runtime):
         self.layer_spec = layer_spec
@@ -36,6 +39,9 @@ class Block:
         self.params = dict(getattr(layer_spec, "params", None) or {})
         self.input_filter = build_part("filter", self.params["input_filter"], rt) \
             if self.params.get("input_filter") is not None else None
+        self.tail = build_part("tail", self.params["tail"], rt) if self.params.get("tail") is not None else None
+        if self.tail is not None and not self.runs_tail:
+            raise ValueError(f"arrangement '{layer_spec.arrangement}' has no place for a tail part")
         want_norms = self.n_norms if self.feed_forward is not None else self.n_norms - 1
         if len(layer_spec.norms) != want_norms:
             raise ValueError(f"arrangement '{layer_spec.arrangement}' needs {want_norms} norms, "
@@ -59,7 +65,7 @@ class Block:
                 nrm.fold_tag = f"fold.{k}"      # scratch of the folded form, one per norm of the block
 
     def parts(self) -> List[Part]:
-        out = [p for p in (self.mixer, self.feed_forward, *self.norms, self.input_filter) if p is not None]
+        out = [p for p in (self.mixer, self.feed_forward, *self.norms, self.input_filter, self.tail) if p is not None]
         if self.position is not None:
             out.append(self.position)
         return out
@@ -99,6 +105,7 @@ class Block:
 
 class PreNormBlock(Block):
     takes_next_norm = True
+    runs_tail = True
 
     def first_norm(self):
         """The norm a block in front of this one may fold into its last product (none when a filter reads the
@@ -108,11 +115,13 @@ class PreNormBlock(Block):
     def parts(self) -> list:
         """The parts this block holds."""
         return [p for p in (self.mixer, self.feed_forward, *self.norms, getattr(self, "position", None),
-                            getattr(self, "input_filter", None)) if p is not None]
+                            getattr(self, "input_filter", None), getattr(self, "tail", None)) if p is not None]
 
     def forward(self, residual: torch.Tensor, pending, ctx, slot: int, write_cache: bool, next_norm=None):
         # only a foldable norm knows ``may_defer`` (hand a folded norm on to a consumer that finishes it)
         has_ffn = self.feed_forward is not None
+        if self.tail is not None:    # the tail reads the stream behind the last part: no norm is folded past it
+            next_norm = None
         defer0 = {"may_defer": True} if self._norm_folds[0] and self._mixer_defers else {}
         defer1 = {"may_defer": True} if has_ffn and self._norm_folds[1] and self._ffn_defers else {}
         if self.input_filter is not None:
@@ -127,7 +136,7 @@ class PreNormBlock(Block):
                 kw["then_norm"] = following
         a = self.mixer.forward(x, ctx, slot, write_cache, **kw)
         if not has_ffn:              # a block of a mixer only: its delta (or folded norm) goes to the next block
-            return residual, a
+            return (residual, a) if self.tail is None else self.tail.forward(residual, a, ctx)
         x = self.norms[1].forward(residual, a, ctx, **defer1)
         kw = {}
         if self._ffn_fuses:
@@ -135,7 +144,7 @@ class PreNormBlock(Block):
             if self._ffn_folds:
                 kw["then_norm"] = next_norm
         f = self.feed_forward.forward(x, ctx, **kw)
-        return residual, f
+        return (residual, f) if self.tail is None else self.tail.forward(residual, f, ctx)
 
 
 class ScaledPreNormBlock(Block):
