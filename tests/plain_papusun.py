@@ -218,3 +218,74 @@ def forward(config: dict, weights: Dict[str, torch.Tensor], tokens: List[int], d
         if streams is not None:
             streams.append(x.clone())
     return (layer_norm(x, w["final.norm"], eps) @ w["head"].T) * float(config["logit_scale"])
+
+
+def greedy_generate(config: dict, weights: Dict[str, torch.Tensor], prompt: List[int], n: int) -> List[int]:
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(torch.argmax(forward(config, weights, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out
+
+
+def tensor_shapes(config: dict) -> Dict[str, tuple]:
+    """Names and shapes of a model's tensors."""
+    W, vocab, n = int(config["width"]), int(config["vocab"]), len(config["layers"])
+    side = int(config["token_side"]["dim"]) if config.get("token_side") else 0
+    out = {"embed": (vocab, W), "final.norm": (W,), "head": (vocab, W)}
+    if side:
+        out["side.embed"] = (vocab, n * side)
+    for i, L in enumerate(config["layers"]):
+        p, mx, m = f"l{i}", L["mixer"], f"l{i}.mix"
+        out[p + ".norm1"] = (W,)
+        if L["type"] == "parallel":
+            a, b = mx["left"], mx["right"]
+            H, G, D, V = int(a["heads"]), int(a["kv_heads"]), int(a["dim"]), int(a["vdim"])
+            out.update({m + ".left.q": (H * D, W), m + ".left.q.b": (H * D,), m + ".left.k": (G * D, W),
+                        m + ".left.k.b": (G * D,), m + ".left.v": (G * V, W), m + ".left.v.b": (G * V,),
+                        m + ".left.o": (W, H * V)})
+            H, G, D, V, c = int(b["heads"]), int(b["kv_heads"]), int(b["dim"]), int(b["vdim"]), int(b["conv"])
+            r = m + ".right"
+            out.update({r + ".q": (G * D, W), r + ".q.conv": (G * D, c), r + ".k": (G * D, W), r + ".k.conv": (G * D, c),
+                        r + ".v": (H * V, W), r + ".v.conv": (H * V, c), r + ".b": (H, W), r + ".A_log": (H,),
+                        r + ".norm": (V,), r + ".a": (H, W), r + ".dt_bias": (H,), r + ".g": (H * V, W),
+                        r + ".o": (W, H * V)})
+        else:
+            H, D, R, V = int(mx["heads"]), int(mx["dim"]), int(mx["rot_dim"]), int(mx["vdim"])
+            kr, qr = int(mx["kv_rank"]), int(mx["q_rank"])
+            out.update({m + ".dq": (qr, W), m + ".dq.norm": (qr,), m + ".uq": (H * (D + R), qr), m + ".uk": (H * D, kr),
+                        m + ".uv": (H * V, kr), m + ".g": (H, W), m + ".o": (W, H * V)})
+            if mx.get("kv_from") is None:
+                out.update({m + ".dkv": (kr + R, W), m + ".dkv.norm": (kr,)})
+        if L.get("mlp") is not None:
+            F = int(L["mlp"]["ff"])
+            out.update({p + ".norm2": (W,), p + ".mlp.gate": (F, W), p + ".mlp.up": (F, W), p + ".mlp.down": (W, F)})
+        if side:
+            out.update({p + ".side.gate": (side, W), p + ".side.proj": (W, side), p + ".side.norm": (W,)})
+    return out
+
+
+def random_weights(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random tensors of a size that keeps every mechanism alive: matrices ~ 1/sqrt(columns), norm weights around
+    one, biases around zero.  Values are rounded to bfloat16 so that a bfloat16 engine holds the same numbers."""
+    gen = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        leaf = name.rsplit(".", 1)[-1]
+        if name in ("embed", "side.embed"):
+            t = torch.randn(shape, generator=gen) * 0.7
+        elif leaf in ("norm1", "norm2", "norm"):
+            t = 1.0 + torch.randn(shape, generator=gen) * 0.2
+        elif leaf == "conv":
+            t = torch.randn(shape, generator=gen) * 0.5
+        elif leaf == "A_log":
+            t = torch.randn(shape, generator=gen) * 0.5 - 1.0
+        elif leaf == "dt_bias" or (leaf == "b" and len(shape) == 1):
+            t = torch.randn(shape, generator=gen) * 0.3
+        else:
+            t = torch.randn(shape, generator=gen) / math.sqrt(shape[-1])
+            if leaf in ("q", "k", "v", "uq", "uk", "dkv"):
+                t = t * 2.0
+        out[name] = t.to(torch.bfloat16).to(torch.float32)
+    return out
