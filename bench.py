@@ -278,9 +278,9 @@ def main() -> int:
     ap.add_argument("--no-decode", action="store_true", help="prefill measurement only (for profiling)")
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="model shape (default: the metric's 8b)")
-    ap.add_argument("--design", default=None, choices=["kolorax", "pepolorn", "kefisun"],
+    ap.add_argument("--design", default=None, choices=["kolorax", "pepolorn", "kefisun", "papusun"],
                     help="instead of the default workload: prefill and decode throughput of this design at a few sizes, "
-                         "beside the closest existing model at equal size (Kolorax beside Qwen3 dense, Pepolorn beside Kolorax, Kefisun beside Qwen3 dense), and its "
+                         "beside the closest existing model at equal size (Kolorax beside Qwen3 dense, Pepolorn beside Kolorax, Kefisun beside Qwen3 dense, Papusun beside Kefisun), and its "
                          "kernels against their floors")
     ap.add_argument("--design-sizes", default="", help="with --design: the sizes to run, with commas (default: all)")
     args = ap.parse_args()

@@ -1,7 +1,7 @@
 """Throughput of a design beside the closest existing model at equal size: Kolorax beside Qwen3 dense, Pepolorn
-beside Kolorax, Kefisun beside Qwen3 dense.
+beside Kolorax, Kefisun beside Qwen3 dense, Papusun beside Kefisun.
 
-``python bench.py --design kolorax`` (or ``pepolorn``, ``kefisun``) calls `main` here; the default workload of bench.py is untouched.
+``python bench.py --design kolorax`` (or ``pepolorn``, ``kefisun``, ``papusun``) calls `main` here; the default workload of bench.py is untouched.
 For each size, both models are built with seeded random weights at layer sizes that resemble a real
 model's (same width, same number of layers, the dense feed-forward as wide as the experts a token
 uses plus the shared one) and run through the engine's own loop (`Engine`: scheduler, captured decode
@@ -292,6 +292,8 @@ def main(args, peaks: dict) -> int:
         return pepolorn_main(args, peaks)
     if args.design == "kefisun":
         return kefisun_main(args, peaks)
+    if args.design == "papusun":
+        return papusun_main(args, peaks)
     out = {"design": "Kolorax", "beside": "Qwen3 dense at equal width, layers and feed-forward width per token",
            "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
            "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
@@ -497,6 +499,204 @@ def kefisun_main(args, peaks: dict) -> int:
         dense = run_engine(qwen3_config(max_len=max_len, **size), args.dtype, args.batch, args.prompt_len, args.steps)
         out["sizes"][name] = {"shape": size, "kefisun": ours, "qwen3": dense,
                               "kernels": kefisun_kernel_table(size["width"], args.batch, args.prompt_len, peaks)}
+        print(json.dumps({"partial": name, **out["sizes"][name]}), flush=True)
+    print(json.dumps(out))
+    return 0
+
+
+# --------------------------------------------------------------------------- #
+# Papusun beside Kefisun
+PAPUSUN_WINDOW = 1024
+
+
+def papusun_config(width: int, layers: int, ff: int, shared_ff: int = 0) -> dict:
+    """Latent-attention layers (heads of 128 + 64 rotated, a latent of 192 for keys and values and of half the width for the
+    queries, a window of 1024 tokens; every second one of them reads the rows of the one in front) with every fourth
+    layer two mixers side by side (attention over every key with heads of 128, four query heads a kv head, half of
+    the head rotated, capped scores; a delta rule with heads of 128 x 128, two heads a q/k head); the dense
+    feed-forward as wide as the model's beside it; a side input of 256 numbers a token and layer."""
+    heads = width // 128
+    lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": max(256, width // 2),
+           "scale": 192 ** -0.5, "mask": {"size": PAPUSUN_WINDOW}, "rot": {"base": 10000.0, "dims": 64}}
+    par = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                    "softcap": 30.0, "rot": {"base": 500000.0, "dims": 64,
+                                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+           "right": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4},
+           "left_scale": 1.0, "right_scale": 1.0}
+    mlp = {"kind": "dense", "ff": TOP * ff + shared_ff}
+    out, last_writer = [], None
+    for i in range(layers):
+        if i % 4 == 2:
+            out.append({"type": "parallel", "mixer": par, "mlp": mlp})
+            continue
+        mx = dict(lat)
+        if last_writer is not None and i % 4 in (1, 3):
+            mx["kv_from"] = last_writer
+        else:
+            last_writer = i
+        out.append({"type": "latent_attention", "mixer": mx, "mlp": mlp})
+    return {"architecture": "Papusun", "vocab": VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "token_side": {"dim": 256}, "layers": out}
+
+
+def papusun_kernel_table(width: int, batch: int, prompt: int, peaks: dict) -> list:
+    """The kernels that Papusun added or changed, alone against their floors, each beside the like kernel (or the
+    same kernel without the new option) of the models that were there."""
+    from .ops import kernels as K
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    flush = torch.empty(192 << 20, dtype=torch.uint8, device=dev)
+    hbm, tflops = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    rows = []
+
+    def add(name, us, bytes_=0, flops=0, like=None):
+        floor = max(bytes_ / hbm, flops / tflops) * 1e6
+        rows.append({"kernel": name, "us": round(us, 1), "floor_us": round(floor, 2), "of_floor": round(floor / us, 3) if us else None,
+                     "bound": "memory" if bytes_ / hbm >= flops / tflops else "tensor", "like": like})
+    H, d, block = width // 128, 128, 16
+    G = max(1, H // 4)
+    C = (H + 2 * G) * d
+    rank, rot, window = 192, 64, PAPUSUN_WINDOW
+    ld = rank + rot
+    for label, n_seqs, q, ctx_len in (("prefill", batch, prompt, 0), ("decode", batch * 8, 1, prompt)):
+        T = n_seqs * q
+        per = -(-(q + ctx_len) // block)
+        ctx = SimpleNamespace(cu_q=torch.arange(0, T + 1, q, dtype=torch.int32, device=dev), num_seqs=n_seqs,
+                              token_seq=torch.arange(T, dtype=torch.int32, device=dev) // q,
+                              positions=(torch.arange(T, dtype=torch.int32, device=dev) % q) + ctx_len,
+                              state_slots=torch.arange(1, n_seqs + 1, dtype=torch.int32, device=dev),
+                              seq_fresh=torch.zeros(n_seqs, dtype=torch.int32, device=dev),
+                              status=torch.zeros(1, dtype=torch.int32, device=dev))
+        ctx_lens = torch.full((n_seqs,), ctx_len, dtype=torch.int32, device=dev)
+        table = (torch.arange(n_seqs * per, dtype=torch.int32, device=dev) + 1).view(n_seqs, per).contiguous()
+        # -- the attention over every key: heads finished (biases, interleaved rotation, cache write), capped scores
+        pages = (torch.randn(n_seqs * per + 1, 2, G, block, d, device=dev) * 0.5).to(bf)
+        qkv = (torch.randn(T, C, device=dev) * 0.5).to(bf)
+        freq = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -torch.arange(32, dtype=torch.float64) / 32).to(dev)
+        bias = torch.randn(C, device=dev) * 0.1
+        us = _time(lambda: K.rope_unit_norm_store(qkv, H, G, d, d, 1e-6, freq, 1.0, ctx, table, pages, interleaved=True,
+                                                  normalize=False, bias=bias), flush=flush)
+        add(f"head finish: biases, interleaved rotation, cache write {label} ({T} rows)", us, T * C * 2 * 2,
+            like="head finish: rotation by halves, unit norm, cache write")
+        us = _time(lambda: K.rope_unit_norm_store(qkv, H, G, d, d, 1e-6, freq, 1.0, ctx, table, pages), flush=flush)
+        add(f"head finish: rotation by halves, unit norm, cache write {label} ({T} rows)", us, T * C * 2 * 2)
+        att = torch.empty(T, H * d, dtype=bf, device=dev)
+        if q > 1:
+            flops = 4 * n_seqs * (q * (q + 1) // 2) * H * d
+            kv_bytes = T * (2 * H + 2 * G) * d * 2
+            tiles = n_seqs * -(-(q * (H // G)) // 128)
+            for name, cap in (("attention tcgen05, every key, capped scores", 30.0), ("attention tcgen05, every key", 0.0)):
+                us = _time(lambda: K.attn_tc(qkv, C, pages, table, ctx.cu_q, ctx_lens, n_seqs, tiles, att, H, G, d, d ** -0.5, 0,
+                                             ctx.status, softcap=cap), flush=flush)
+                add(f"{name} {label}", us, kv_bytes, flops, like="attention tcgen05, every key" if cap else None)
+        else:
+            keys = ctx_len + 1
+            splits = K.decode_splits(n_seqs, G, keys)
+            part_o = torch.empty(n_seqs * H * splits * d, device=dev)
+            part_ml = torch.empty(n_seqs * H * splits * 2, device=dev)
+            kv_bytes = n_seqs * keys * 2 * G * d * 2 + T * 2 * H * d * 2
+            for name, cap in (("attention decode, every key, capped scores", 30.0), ("attention decode, every key", 0.0)):
+                us = _time(lambda: K.attn_decode(qkv, C, pages, table, ctx.cu_q, ctx_lens, n_seqs, att, part_o, part_ml, H, G, d,
+                                                 d ** -0.5, 0, splits, ctx.status, None, cap), flush=flush)
+                add(f"{name} ({n_seqs} x {keys} keys)", us, kv_bytes, like="attention decode, every key" if cap else None)
+        # -- the delta rule with one decay a head beside the one with a decay a key channel
+        dh, dg, N, V, taps = H, max(1, H // 2), 128, 128, 4
+        DC = 2 * dg * N + dh * V
+        sf = K.delta_state_floats(dh, N, V)
+        dstate = torch.zeros(n_seqs + 1, sf + (taps - 1) * DC, dtype=torch.float32, device=dev)
+        dproj = (torch.randn(T, DC + dh, device=dev) * 0.5).to(bf)
+        dqkv = (torch.randn(T, DC, device=dev) * 0.5).to(bf)
+        do = torch.empty(T, dh * V, device=dev)
+        io = T * (DC * 2 + dh * V * 4) + 2 * n_seqs * dh * N * V * 4
+        for name, per_head in (("delta rule, a decay a head", True), ("delta rule, a decay a key channel", False)):
+            rows_a = dh if per_head else dh * N
+            ag = torch.randn(T, rows_a + dh * V, device=dev)
+            dtb, al = torch.zeros(rows_a, device=dev), torch.zeros(dh, device=dev)
+            us = _time(lambda: K.delta_rule_scan((dqkv, 0), (dqkv, dg * N), (dqkv, 2 * dg * N), (dproj, DC), (ag, 0), dtb, al, dstate, 0, ctx,
+                                                 do, dh, N, V, heads_per_group=dh // dg, q_scale=N ** -0.5, decay_per_head=per_head),
+                       flush=flush)
+            add(f"{name} {label} ({n_seqs} x {q})", us, io + T * rows_a * 4, like=None if not per_head else "delta rule, a decay a key channel")
+            dy = torch.empty(T, dh * V, dtype=bf, device=dev)
+            nw = torch.ones(V, device=dev)
+            act = "silu" if per_head else "sigmoid"
+            us = _time(lambda: K.head_norm_gate(do, (ag, rows_a), nw, 1e-6, dy, dh, V, act), flush=flush)
+            add(f"head norm and {act} gate {label} ({T} rows)", us, T * dh * V * (4 + 4 + 2),
+                like="head norm and sigmoid gate" if per_head else None)
+        # -- latent attention: queries finished and rows written, attention inside a window over one-plane pages, head gates
+        lpages = (torch.randn(n_seqs * per + 1, 1, 1, block, ld, device=dev) * 0.5).to(bf)
+        lq = (torch.randn(T, H * (d + rot), device=dev) * 0.5).to(bf)
+        dkv = (torch.randn(T, ld, device=dev) * 0.5).to(bf)
+        q_abs = (torch.randn(H, T, rank, device=dev) * 0.5).to(bf)
+        q_full = torch.empty(T, H * ld, dtype=bf, device=dev)
+        cn = torch.ones(rank, device=dev)
+        for name, inter in (("latent rows and queries, interleaved rotation", True), ("latent rows and queries, rotation by halves", False)):
+            us = _time(lambda: K.latent_finish(lq, dkv, q_abs, cn, 1e-6, freq, ctx, table, lpages, q_full, H, d, rot, rank, rot, inter),
+                       flush=flush)
+            add(f"{name} {label} ({T} rows)", us, T * (H * (d + rot) + ld + 2 * H * rank + H * rot + ld) * 2,
+                like=None if not inter else "latent rows and queries, rotation by halves")
+        latt = torch.empty(T, H * ld, dtype=bf, device=dev)
+        for name, win in (("latent attention inside a window", window), ("latent attention over every key", 0)):
+            keys_seen = sum(min(win or (1 << 30), i + 1 + ctx_len) for i in range(q)) * n_seqs
+            step_ctx = SimpleNamespace(**vars(ctx), ctx_lens=ctx_lens, q_lens=[q] * n_seqs, ctx_lens_host=[ctx_len] * n_seqs,
+                                       num_decode_seqs=n_seqs if q == 1 else 0, max_kv_len=q + ctx_len, ranges_by_length=False,
+                                       workspace=_Scratch(dev), captured=False, memo={}, key_share_level=0)
+            us = _time(lambda: K.paged_attention(q_full, H * ld, lpages, table, step_ctx, latt, H, 1, ld, 192 ** -0.5, win), flush=flush)
+            kv_b = (n_seqs * min(win or (1 << 30), q + ctx_len) * ld * 2 if q == 1 else T * ld * 2) + T * 2 * H * ld * 2
+            add(f"{name} {label}", us, kv_b, 2 * keys_seen * H * (ld + rank), like=None if not win else "latent attention over every key")
+        val = (torch.randn(H, T, d, device=dev) * 0.5).to(bf)
+        y = torch.empty(T, H * d, dtype=bf, device=dev)
+        for name, per_head in (("latent head gates, one a head", True), ("latent head gates, one an element", False)):
+            g = (torch.randn(T, H if per_head else H * d, device=dev)).to(bf)
+            us = _time(lambda: K.latent_gate(val, g, y, H, d, per_head), flush=flush)
+            add(f"{name} {label} ({T} rows)", us, T * H * d * 2 * 2 + g.numel() * 2, like=None if not per_head else "latent head gates, one an element")
+        # -- the token's side input: gated table rows, and the norm that adds the result to the stream
+        side = 256
+        tbl = (torch.randn(VOCAB, 8 * side, device=dev) * 0.5).to(bf)
+        ids = torch.randint(0, VOCAB, (T,), dtype=torch.int32, device=dev)
+        gate, gout = (torch.randn(T, side, device=dev)).to(bf), torch.empty(T, side, dtype=bf, device=dev)
+        us = _time(lambda: K.act_mul_table_rows(gate, ids, tbl, 3 * side, gout, "gelu_tanh", ctx.status), flush=flush)
+        add(f"side input: GELU gate times table rows {label} ({T} rows)", us, T * side * 2 * 3, like="silu_mul")
+        gu, act_o = (torch.randn(T, 2 * side, device=dev)).to(bf), torch.empty(T, side, dtype=bf, device=dev)
+        us = _time(lambda: K.silu_mul(gu, act_o), flush=flush)
+        add(f"silu_mul {label} ({T} rows of {side})", us, T * side * 2 * 3)
+        res, yy, nw2 = torch.randn(T, width, device=dev), torch.randn(T, width, device=dev), torch.ones(width, device=dev)
+        us = _time(lambda: K.norm_add(res, yy, nw2, 1e-6), flush=flush)
+        add(f"side input: RMS norm added to the stream {label} ({T} rows)", us, T * width * 4 * 3, like="layer norm with the residual add")
+        out_n, lw = torch.empty(T, width, dtype=bf, device=dev), torch.ones(width, device=dev)
+        us = _time(lambda: K.add_layer_norm(res, yy, lw, None, 1e-6, out_n, None, 1.0), flush=flush)
+        add(f"layer norm with the residual add {label} ({T} rows)", us, T * width * (4 * 3 + 2))
+    return rows
+
+
+class _Scratch:
+    """Named scratch buffers for a kernel timed alone (the engine's workspace in small)."""
+
+    def __init__(self, device):
+        self.device, self._bufs = device, {}
+
+    def get(self, tag, shape, dtype):
+        n = 1
+        for s_ in shape:
+            n *= int(s_)
+        buf = self._bufs.get((tag, dtype))
+        if buf is None or buf.numel() < n:
+            buf = self._bufs[(tag, dtype)] = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+        return buf[:n].view(*shape)
+
+
+def papusun_main(args, peaks: dict) -> int:
+    out = {"design": "Papusun", "beside": "Kefisun at equal width, layers and feed-forward width (six of Papusun's eight layers are latent "
+                                          f"attention inside a window of {PAPUSUN_WINDOW}, two are attention over every key beside a delta rule; "
+                                          "two of Kefisun's eight layers are recurrent and have no feed-forward)",
+           "dtype": args.dtype, "batch": args.batch, "prompt_len": args.prompt_len, "new_tokens": args.steps,
+           "data": "synthetic token ids, seeded random weights", "peaks": peaks.get("source"), "sizes": {}}
+    for name, size in SIZES.items():
+        if args.design_sizes and name not in args.design_sizes.split(","):
+            continue
+        ours = run_engine(papusun_config(**size), args.dtype, args.batch, args.prompt_len, args.steps)
+        beside = run_engine(kefisun_config(**size), args.dtype, args.batch, args.prompt_len, args.steps)
+        out["sizes"][name] = {"shape": size, "papusun": ours, "kefisun": beside,
+                              "kernels": papusun_kernel_table(size["width"], args.batch, args.prompt_len, peaks)}
         print(json.dumps({"partial": name, **out["sizes"][name]}), flush=True)
     print(json.dumps(out))
     return 0

