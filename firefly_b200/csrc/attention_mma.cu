@@ -124,10 +124,11 @@ struct WarpState {
         for (int i = 0; i < D / 8; ++i) { o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f; }
         m[0] = m[1] = -CUDART_INF_F;
         l[0] = l[1] = 0.f;
-        cap = 0.f;
+        cap = cap_k = 0.f;
     }
     // a cap on the scores (in the units of the scaled scores, log2 e included; 0: none): v <- cap * tanh(v / cap)
-    float cap;
+    float cap, cap_k;
+    __device__ __forceinline__ void set_cap(float c) { cap = c; cap_k = c != 0.f ? 2.0f * LOG2E / c : 0.f; }
 
     // Qs: this warp's 16 rows of q in smem ([16][KSTR]); Ks/Vs: this warp's KN keys.
     // key0: absolute index of the warp's first key.  Row r of the fragment (g, g+8)
@@ -165,7 +166,7 @@ struct WarpState {
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 float v = s[j][e] * scale_log2;
-                if (cap != 0.f) v = capped_score(v, cap);
+                if (cap != 0.f) v = capped_score(v, cap, cap_k);
                 const int key = key0 + j * 8 + 2 * t4 + (e & 1);
                 bool visible = true;
                 if (need_mask) {
@@ -329,7 +330,7 @@ attn_tiled_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restri
 
     WarpState<BN> st;
     st.init();
-    st.cap = softcap_log2;
+    st.set_cap(softcap_log2);
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {
@@ -667,7 +668,7 @@ attn_decode_body(const bf16* __restrict__ q, int q_stride, const bf16* __restric
     }
     WarpState<16> st;
     st.init();
-    st.cap = hd.softcap_log2;
+    st.set_cap(hd.softcap_log2);
     for (int t = t_begin; t < t_end; ++t) {
         const int buf = (t - t_begin) & 1;
         if (t + 1 < t_end) {

@@ -373,6 +373,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
         // the same holds for a cap on the scores (softcap_log2, in the scaled scores' units; 0: none)
         const bool early = dist_bias != nullptr || softcap_log2 != 0.f;
         const float sl2 = early ? 1.0f : scale_log2;
+        const float cap_k = softcap_log2 != 0.f ? 2.0f * LOG2E / softcap_log2 : 0.f;
         float m = -CUDART_INF_F, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_tiles && ok; ++j) {
@@ -394,7 +395,7 @@ attn_tc_kernel(const __grid_constant__ TensorMapArg kv_map, const bf16* __restri
                 for (int i = 0; i < BN; ++i) {
                     const int key = key0 + i;
                     float v = s[i] * scale_log2;
-                    if (softcap_log2 != 0.f) v = capped_score(v, softcap_log2);
+                    if (softcap_log2 != 0.f) v = capped_score(v, softcap_log2, cap_k);
                     if (key < lo || key >= hi) v = -CUDART_INF_F;
                     else if (brow) v -= __ldg(brow - key) * LOG2E;
                     s[i] = v;

@@ -76,7 +76,9 @@ class GatedMLP(Part):
     tensors' leaves under the prefix as parameters (``gate_leaf``, ``up_leaf``, ``down_leaf``).  Gate and up are one
     product against the stacked matrix [gate rows | up rows]; the activation is a kernel of its own.  With
     ``bias`` every projection has a bias (leaf + ``bias_suffix``), added in 32-bit: gate's and up's where the
-    activation reads them, down's into the 32-bit stream.
+    activation reads them, down's into the 32-bit stream.  With SiLU and no biases it is the SwiGLU feed-forward under
+    other tensor names, and runs as that one does: in bfloat16 the stacked matrix interleaves gate and up rows in groups
+    of 16 and steps of few tokens take the activation in the product's epilogue.
 
     Parameters: hidden_size, intermediate_size, activation, limit, bias, bias_suffix."""
 
@@ -96,6 +98,12 @@ class GatedMLP(Part):
         if self.activation == "clamped_swish" and not (self.limit > 0):
             raise ValueError(f"{self.prefix}: the clamped activation needs a positive limit")
         self.w_gate_up = self.w_down = self.b_gate_up = self.b_down = None
+        self.swiglu = self.activation == "silu" and not self.has_bias      # the fused SwiGLU path serves it
+        self.interleaved = False
+
+    def _interleaves(self, gate_dtype, up_dtype) -> bool:
+        return self.swiglu and gate_dtype == up_dtype == torch.bfloat16 and self.rt.dtype == torch.bfloat16 \
+            and self.inter % 16 == 0
 
     def weight_specs(self) -> List[WeightSpec]:
         g, u, d = (self.name(leaf) for leaf in self.leaves)
@@ -110,17 +118,23 @@ class GatedMLP(Part):
 
     def fused_layout(self, dtype_of) -> List[FusedSpec]:
         g, u, _ = (self.name(leaf) for leaf in self.leaves)
-        return [FusedSpec(self.name("gate_up"), (2 * self.inter, self.hidden), (Piece(g, 0), Piece(u, self.inter)))]
+        if self._interleaves(dtype_of(g), dtype_of(u)):
+            pieces = (Piece(g, 0, 16, 32), Piece(u, 16, 16, 32))
+        else:
+            pieces = (Piece(g, 0), Piece(u, self.inter))
+        return [FusedSpec(self.name("gate_up"), (2 * self.inter, self.hidden), pieces)]
 
     def bind(self, tensors: Mapping[str, torch.Tensor]) -> None:
         g, u, d = (self.name(leaf) for leaf in self.leaves)
         if self.name("gate_up") in tensors:
             self.w_gate_up = self._matrix(tensors[self.name("gate_up")])
+            self.interleaved = self._interleaves(self.w_gate_up.dtype, self.w_gate_up.dtype)
         else:
             a, b = self._matrix(tensors[g]), self._matrix(tensors[u])
             if a.dtype != b.dtype:
                 a, b = a.to(torch.float32), b.to(torch.float32)
-            self.w_gate_up = torch.cat([a, b], dim=0).contiguous()
+            self.interleaved = self._interleaves(a.dtype, b.dtype)
+            self.w_gate_up = K.interleave_gate_up(a, b) if self.interleaved else torch.cat([a, b], dim=0).contiguous()
         self.w_down = self._matrix(tensors[d])
         if self.has_bias:
             sfx = self.bias_suffix
@@ -129,6 +143,9 @@ class GatedMLP(Part):
 
     def forward(self, x, ctx, accumulate_into=None):
         T = x.shape[0]
+        if self.swiglu:
+            act = linear_swiglu(x, self.w_gate_up, self.inter, self.interleaved, ctx)
+            return linear_into_residual(act, self.w_down, accumulate_into, ctx, "mlp.down")
         gu = ctx.workspace.get("mlp.gate_up", (T, 2 * self.inter), ctx.dtype)
         apply_linear(x, self.w_gate_up, gu, ctx, "mlp.gate_up")
         act = ctx.workspace.get("mlp.act", (T, self.inter), ctx.dtype)
