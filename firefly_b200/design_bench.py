@@ -519,8 +519,8 @@ def papusun_config(width: int, layers: int, ff: int, shared_ff: int = 0) -> dict
     lat = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 192, "q_rank": max(256, width // 2),
            "scale": 192 ** -0.5, "mask": {"size": PAPUSUN_WINDOW}, "rot": {"base": 10000.0, "dims": 64}}
     par = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
-                    "softcap": 30.0, "rot": {"base": 500000.0, "dims": 64,
-                                             "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}},
+                    "softcap": 50.0, "rot": {"base": 500000.0, "dims": 64,
+                                             "scaling": {"factor": 16.0, "low": 1.0, "high": 8.0, "original": 8192}}},
            "right": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "conv": 4},
            "left_scale": 1.0, "right_scale": 1.0}
     mlp = {"kind": "dense", "ff": TOP * ff + shared_ff}
@@ -585,7 +585,7 @@ def papusun_kernel_table(width: int, batch: int, prompt: int, peaks: dict) -> li
             flops = 4 * n_seqs * (q * (q + 1) // 2) * H * d
             kv_bytes = T * (2 * H + 2 * G) * d * 2
             tiles = n_seqs * -(-(q * (H // G)) // 128)
-            for name, cap in (("attention tcgen05, every key, capped scores", 30.0), ("attention tcgen05, every key", 0.0)):
+            for name, cap in (("attention tcgen05, every key, capped scores", 50.0), ("attention tcgen05, every key", 0.0)):
                 us = _time(lambda: K.attn_tc(qkv, C, pages, table, ctx.cu_q, ctx_lens, n_seqs, tiles, att, H, G, d, d ** -0.5, 0,
                                              ctx.status, softcap=cap), flush=flush)
                 add(f"{name} {label}", us, kv_bytes, flops, like="attention tcgen05, every key" if cap else None)
@@ -595,7 +595,7 @@ def papusun_kernel_table(width: int, batch: int, prompt: int, peaks: dict) -> li
             part_o = torch.empty(n_seqs * H * splits * d, device=dev)
             part_ml = torch.empty(n_seqs * H * splits * 2, device=dev)
             kv_bytes = n_seqs * keys * 2 * G * d * 2 + T * 2 * H * d * 2
-            for name, cap in (("attention decode, every key, capped scores", 30.0), ("attention decode, every key", 0.0)):
+            for name, cap in (("attention decode, every key, capped scores", 50.0), ("attention decode, every key", 0.0)):
                 us = _time(lambda: K.attn_decode(qkv, C, pages, table, ctx.cu_q, ctx_lens, n_seqs, att, part_o, part_ml, H, G, d,
                                                  d ** -0.5, 0, splits, ctx.status, None, cap), flush=flush)
                 add(f"{name} ({n_seqs} x {keys} keys)", us, kv_bytes, like="attention decode, every key" if cap else None)
