@@ -230,7 +230,7 @@ def test_layer_norm_without_a_bias_alone(tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("tokens,side,layer", [(1, 6, 0), (5, 1, 1), (150, 20, 1), (70, 7, 2)])
+@pytest.mark.parametrize("tokens,side,layer", [(1, 6, 0), (5, 1, 1), (32, 12, 2), (33, 12, 0), (150, 20, 1), (70, 7, 2)])
 def test_token_side_alone_reads_its_own_columns_of_the_table(tmp_path, dtype, tokens, side, layer):
     layers = [_with(_lat(1, 8, 8, 8, 8, 8, 4), None)] * 3
     cfg, w, sess = _one_layer(tmp_path, layers, dtype=dtype, side=side)
