@@ -150,6 +150,28 @@ def test_replay_in_every_cutting_matches_the_plain_model(tmp_path, name, dtype):
         assert not sess.cache.live
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_requests_at_middling_sizes(tmp_path, dtype):
+    """Requests of hundreds of tokens (whole, with a decoded tail, and mixed on reused pages and slots) through a model
+    whose attention layers take, in bfloat16, the tcgen05 kernel (cache rows of 64 and 256, heads of 64) and the
+    mma.sync kernel (heads of 80), with windows that end inside the prompts."""
+    cfg = _cfg([_with(_lat(4, 24, 8, 40, 56, 48, 50), _dense(128)),
+                _with(_par(_left(6, 2, 40, 80, dims=20), _right(4, 2, 24, 40, conv=4)), _dense(128)),
+                _with(_lat(3, 16, 8, 24, 56, 24, 70, kv_from=0), None),
+                _with(_par(_left(4, 4, 64, 32, dims=64, softcap=4.0), _right(2, 1, 64, 64)), _dense(96)),
+                _with(_lat(2, 64, 64, 64, 192, 32, 33), _dense(128))], width=96, vocab=211, side=16)
+    model_dir, w = _model_dir(tmp_path, "middling", cfg, seed=3)
+    reqs = U.make_requests(cfg["vocab"], [600, 260, 90], 9)
+    plain = {rid: P.forward(cfg, w, toks).numpy() for rid, toks in reqs.items()}
+    twice = dict(reqs, **{"r1#2": reqs["r1"]})
+    for label, steps in (("whole", U.trace_whole(reqs)), ("decode", U.trace_tail_decode(reqs, tail=48)),
+                         ("mixed", U.trace_mixed(twice, seed=5, max_live=3, sizes=(64, 2, 129, 31, 3, 200)))):
+        sess = _session(model_dir, dtype, U.peak_tokens(steps))
+        _check(U.run_trace(sess, steps), plain, dtype, f"middling/{dtype}/{label}")
+        sess.cache.check()
+        assert not sess.cache.live
+
+
 def test_the_stream_matches_after_every_layer(tmp_path):
     cfg = CONFIGS["both_mixers"]
     model_dir, w = _model_dir(tmp_path, "stream", cfg)
